@@ -42,10 +42,12 @@ def pages_for(n_tokens: int) -> int:
 @dataclass(frozen=True)
 class KVRequest:
     """Keys and values of ``n_kv_heads`` heads of ``head_dim`` lanes for every
-    position (``window`` 0) or for the last ``window`` positions."""
+    position (``window`` 0) or for the last ``window`` positions.  ``v_head_dim``: lanes of a value head when
+    they differ from a key head's (0: the same)."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    v_head_dim: int = 0
 
 
 @dataclass(frozen=True)
@@ -62,9 +64,9 @@ class KVGroup:
         self.request = request
         self.entries = list(entries)
         self.n_pages = n_pages
-        shape = (len(entries), n_pages, request.n_kv_heads, PAGE, request.head_dim)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        shape = (len(entries), n_pages, request.n_kv_heads, PAGE)
+        self.k = torch.zeros(shape + (request.head_dim,), dtype=dtype, device=device)
+        self.v = torch.zeros(shape + (request.v_head_dim or request.head_dim,), dtype=dtype, device=device)
         self.pool = IndexPool(n_pages, "cache page")
         self.tables: Dict[int, List[int]] = {}  # slot -> page ids by page index, -1 = given back
 
@@ -97,7 +99,7 @@ class KVGroup:
                 self.pool.give_back(p)
 
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + self.v.numel()) * self.k.element_size()
 
 
 class Cache:
@@ -137,7 +139,8 @@ class Cache:
             elif kv is not None:
                 by_request.setdefault(kv, []).append(i)
         esize = torch.empty((), dtype=dtype).element_size()
-        need = sum(2 * len(e) * self.n_pages * kv.n_kv_heads * PAGE * kv.head_dim * esize for kv, e in by_request.items())
+        need = sum(len(e) * self.n_pages * kv.n_kv_heads * PAGE * (kv.head_dim + (kv.v_head_dim or kv.head_dim)) * esize
+                   for kv, e in by_request.items())
         for kv, entries in by_request.items():
             g = len(self.groups)
             with translating_oom(f"a cache of {self.max_tokens} tokens ({need / 2 ** 30:.2f} GiB of keys and values "

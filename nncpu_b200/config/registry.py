@@ -40,9 +40,13 @@ def config_class(name: str) -> type:
 
 
 def config_from_dict(d: dict):
+    """The configuration class is chosen by ``"architectures": ["Name", ...]`` (its first entry) or, in files
+    that name one design only, by ``"architecture": "Name"``."""
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        archs = [d["architecture"]]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise BadFormat('config.json has no "architectures": ["..."] entry')
+        raise BadFormat('config.json has neither an "architectures": ["..."] nor an "architecture": "..." entry')
     return config_class(archs[0]).from_dict(d)
 
 

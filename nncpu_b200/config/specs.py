@@ -18,11 +18,14 @@ from typing import Optional, Tuple
 
 @dataclass(frozen=True)
 class NormSpec:
-    """A normalisation over a vector of ``size`` lanes, weights at ``name``."""
+    """A normalisation over a vector of ``size`` lanes, weights at ``name + suffix``.  ``offset`` is added to
+    the stored weight before it multiplies (1.0 for weights that are stored around zero)."""
     kind: str
     size: int
     eps: float
     name: str  # tensor name prefix, e.g. "model.layers.0.input_layernorm"
+    suffix: str = ".weight"
+    offset: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -57,6 +60,25 @@ class AttentionSpec(MixerSpec):
     window: int = 0                  # 0: every earlier key; n: the last n keys up to the query
     qk_norm: Optional[NormSpec] = None   # per-head norm of q and k (names end in q_norm / k_norm)
     position: Optional[PositionSpec] = None
+    v_head_dim: int = 0              # lanes of a value head (and of a head's output); 0: head_dim
+    slope_base: float = 0.0          # b != 0: head h takes 2^(-b (h + 1) / n_heads) * (i - j) off its scaled scores
+    q_temp_coef: float = 0.0         # c != 0: the query at position p is multiplied by
+    q_temp_every: int = 1            # 1 + c * ln(floor((p + 1) / every) + 1)
+    tensor_names: str = "proj"       # "proj": <name>.q_proj.weight / .bias ...; "short": <name>.q, <name>.q.b, ... <name>.o
+
+
+@dataclass(frozen=True)
+class GatedLinearAttentionSpec(MixerSpec):
+    """A recurrent mixer: per head a state of ``key_dim`` x ``value_dim`` numbers that decays per key channel by
+    sigmoid(z)^(1/tau), z from a low-rank projection (``gate_rank``) with a bias; the heads' outputs are
+    RMS-normed (``eps``), gated by silu of a projection and projected back."""
+    hidden_size: int = 0
+    n_heads: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    gate_rank: int = 0
+    tau: float = 1.0
+    eps: float = 1e-6
 
 
 @dataclass(frozen=True)
@@ -74,14 +96,27 @@ class GatedMlpSpec(FeedForwardSpec):
 
 
 @dataclass(frozen=True)
+class DenseMlpSpec(FeedForwardSpec):
+    """down(act(up(x))) with biases on both products; ``activation`` "xielu" has two learned numbers at
+    ``<name>.act``."""
+    hidden_size: int = 0
+    intermediate_size: int = 0
+    activation: str = "xielu"
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer: its parts and their arrangement.  ``kind`` "prenorm":
-    x += mixer(norm1(x)); x += feed_forward(norm2(x))."""
+    x += mixer(norm1(x)); x += feed_forward(norm2(x)).  ``kind`` "sandwich" norms each sublayer's output too:
+    x += norm1_post(mixer(norm1(x))); x += norm2_post(feed_forward(norm2(x))), and a layer without a
+    feed-forward (``feed_forward`` None) has the first sublayer only."""
     kind: str
     norm1: NormSpec
     mixer: MixerSpec
-    norm2: NormSpec
-    feed_forward: FeedForwardSpec
+    norm2: Optional[NormSpec] = None
+    feed_forward: Optional[FeedForwardSpec] = None
+    norm1_post: Optional[NormSpec] = None
+    norm2_post: Optional[NormSpec] = None
 
 
 @dataclass(frozen=True)
@@ -96,10 +131,13 @@ class ScheduleEntry:
 
 @dataclass(frozen=True)
 class EmbeddingSpec:
-    name: str          # tensor name of the table, without ".weight"
+    name: str          # tensor name of the table, without the suffix
     vocab_size: int
     hidden_size: int
     scale: float = 1.0
+    suffix: str = ".weight"
+    positions: Optional[str] = None   # tensor name of a table of learned position vectors [n_positions, hidden],
+    n_positions: int = 0              # added (unscaled) to the embedding rows; sequences cannot outgrow it
 
 
 @dataclass(frozen=True)
@@ -107,10 +145,12 @@ class OutputSpec:
     """Final norm and vocabulary projection.  ``tied`` uses the embedding
     table as the output matrix."""
     norm: NormSpec
-    name: str          # tensor name of the output matrix, without ".weight"
+    name: str          # tensor name of the output matrix, without the suffix
     tied: bool
     vocab_size: int
     hidden_size: int
+    suffix: str = ".weight"
+    softcap: float = 0.0   # c > 0: logits <- c * tanh(logits / c)
 
 
 @dataclass(frozen=True)

@@ -20,37 +20,55 @@
 
 // ---------------------------------------------------------------------------
 // Embedding rows: out[t, :] = table[ids[t], :] * scale, float32 out.
-// A negative id (a padded row) gives zeros.
+// A negative id (a padded row) gives zeros.  With a table of learned position
+// vectors, out[t, :] += pos_table[pos[t], :] (not scaled); a position beyond
+// the table gives NaN rows, which nobody can mistake for a result.
 // ---------------------------------------------------------------------------
 __global__ void embed_kernel(const void* __restrict__ table, int table_dt, const int* __restrict__ ids,
-                             float* __restrict__ out, int hidden, float scale) {
+                             float* __restrict__ out, int hidden, float scale, const void* __restrict__ pos_table,
+                             int pos_dt, const int* __restrict__ pos, int n_pos) {
     const int t = blockIdx.x;
     const int id = ids[t];
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-        out[(size_t)t * hidden + i] = id < 0 ? 0.0f : ld_f(table, (size_t)id * hidden + i, table_dt) * scale;
+    const int p = pos_table != nullptr ? pos[t] : 0;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = 0.0f;
+        if (id >= 0) {
+            v = ld_f(table, (size_t)id * hidden + i, table_dt) * scale;
+            if (pos_table != nullptr)
+                v = (p >= 0 && p < n_pos) ? v + ld_f(pos_table, (size_t)p * hidden + i, pos_dt) : __int_as_float(0x7FC00000);
+        }
+        out[(size_t)t * hidden + i] = v;
+    }
 }
 
 extern "C" int nncpu_embed(const void* table, int table_dt, const int* ids, float* out, int n_tok, int hidden,
-                           int vocab, float scale, void* stream) {
+                           int vocab, float scale, const void* pos_table, int pos_dt, const int* pos, int n_pos,
+                           void* stream) {
     NN_CHECK(n_tok >= 0 && hidden > 0 && vocab > 0, "embed: n_tok %d, hidden %d, vocab %d", n_tok, hidden, vocab);
+    NN_CHECK(pos_table == nullptr || (pos != nullptr && n_pos > 0), "embed: a position table without positions");
     if (n_tok == 0) return 0;
-    embed_kernel<<<n_tok, 256, 0, (cudaStream_t)stream>>>(table, table_dt, ids, out, hidden, scale);
+    embed_kernel<<<n_tok, 256, 0, (cudaStream_t)stream>>>(table, table_dt, ids, out, hidden, scale, pos_table, pos_dt,
+                                                          pos, n_pos);
     NN_LAUNCH_OK("embed");
     return 0;
 }
 
 // ---------------------------------------------------------------------------
-// RMSNorm over the last axis: y = (x * scale) * gamma,
+// RMSNorm over the last axis: y = (x * scale) * (gamma + gamma_offset),
 // scale = 1 / sqrt(mean(x^2) + eps).  `rows` (optional) picks input rows, so
-// the final norm runs only on the rows whose logits are wanted.
+// the final norm runs only on the rows whose logits are wanted.  gamma_offset
+// is 1 for weights that are stored around zero.  With `accumulate` the result
+// is added to y (a norm that closes a sublayer: y is the residual stream).
 // ---------------------------------------------------------------------------
 __global__ void rmsnorm_kernel(const void* __restrict__ x, int x_dt, const void* __restrict__ gamma, int g_dt,
-                               void* __restrict__ y, int y_dt, const int* __restrict__ rows, int dim, float eps) {
+                               void* __restrict__ y, int y_dt, const int* __restrict__ rows, int dim, float eps,
+                               float gamma_offset, int accumulate) {
     __shared__ float scratch[33];
     const int r_out = blockIdx.x;
     const int r_in = rows ? rows[r_out] : r_out;
     if (r_in < 0) {
-        for (int i = threadIdx.x; i < dim; i += blockDim.x) st_f(y, (size_t)r_out * dim + i, y_dt, 0.0f);
+        if (!accumulate)
+            for (int i = threadIdx.x; i < dim; i += blockDim.x) st_f(y, (size_t)r_out * dim + i, y_dt, 0.0f);
         return;
     }
     const size_t base = (size_t)r_in * dim;
@@ -62,8 +80,10 @@ __global__ void rmsnorm_kernel(const void* __restrict__ x, int x_dt, const void*
     ss = block_sum(ss, scratch);
     const float scale = 1.0f / sqrtf(ss * (1.0f / (float)dim) + eps);
     for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-        const float v = ld_f(x, base + i, x_dt) * scale;
-        st_f(y, (size_t)r_out * dim + i, y_dt, gamma ? v * ld_f(gamma, i, g_dt) : v);
+        float v = ld_f(x, base + i, x_dt) * scale;
+        if (gamma) v *= ld_f(gamma, i, g_dt) + gamma_offset;
+        const size_t at = (size_t)r_out * dim + i;
+        st_f(y, at, y_dt, accumulate ? ld_f(y, at, y_dt) + v : v);
     }
 }
 
@@ -118,10 +138,12 @@ rmsnorm_f32_kernel(const float* __restrict__ x, const void* __restrict__ gamma, 
 }
 
 extern "C" int nncpu_rmsnorm(const void* x, int x_dt, const void* gamma, int g_dt, void* y, int y_dt,
-                             const int* rows, int n_rows, int dim, float eps, void* stream) {
+                             const int* rows, int n_rows, int dim, float eps, float gamma_offset, int accumulate,
+                             void* stream) {
     NN_CHECK(n_rows >= 0 && dim > 0, "rmsnorm: %d rows of %d", n_rows, dim);
+    NN_CHECK(!accumulate || x != y, "rmsnorm: a norm cannot be added to its own input");
     if (n_rows == 0) return 0;
-    if (x_dt == DT_F32 && dim % 4 == 0 && dim >= 1024 && dim <= 256 * 4 * 8 && (uintptr_t)x % 16 == 0 &&
+    if (gamma_offset == 0.0f && !accumulate && x_dt == DT_F32 && dim % 4 == 0 && dim >= 1024 && dim <= 256 * 4 * 8 && (uintptr_t)x % 16 == 0 &&
         (uintptr_t)y % 16 == 0) {
         const float* xf = (const float*)x;
         cudaLaunchConfig_t cfg = {};
@@ -137,7 +159,8 @@ extern "C" int nncpu_rmsnorm(const void* x, int x_dt, const void* gamma, int g_d
         return 0;
     }
     int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : (dim >= 128 ? 128 : 32));
-    rmsnorm_kernel<<<n_rows, threads, 0, (cudaStream_t)stream>>>(x, x_dt, gamma, g_dt, y, y_dt, rows, dim, eps);
+    rmsnorm_kernel<<<n_rows, threads, 0, (cudaStream_t)stream>>>(x, x_dt, gamma, g_dt, y, y_dt, rows, dim, eps,
+                                                                 gamma_offset, accumulate);
     NN_LAUNCH_OK("rmsnorm");
     return 0;
 }
@@ -256,10 +279,12 @@ extern "C" int nncpu_rope_table(const int* pos, const float* inv_freq, float* cs
 
 // ---------------------------------------------------------------------------
 // Per-head q/k RMSNorm, rotation, and the append of k and v to the cache.
-// qkv [n_tok, (n_heads + 2 n_kv) * hd] holds q heads, then k heads, then v
-// heads.  One warp per (token, head).  q goes to q_out [n_tok, n_heads * hd];
-// k (normed, rotated) and v (raw) go to their page rows.  With n_kv == 0 the
-// mixer reads another layer's cache and only q is processed.
+// qkv [n_tok, (n_heads + n_kv) * hd + n_kv * vd] holds q heads, then k heads,
+// then v heads (of vd lanes each).  One warp per (token, head).  q goes to
+// q_out [n_tok, n_heads * hd]; k (normed, rotated) and v (raw) go to their page
+// rows.  With n_kv == 0 the mixer reads another layer's cache and only q is
+// processed.  A query temperature (temp_coef != 0) multiplies the query at
+// position p by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1).
 // ---------------------------------------------------------------------------
 __global__ void qk_norm_rope_append_kernel(const void* __restrict__ qkv, int in_dt, const void* __restrict__ q_gamma,
                                            const void* __restrict__ k_gamma, int g_dt, float eps,
@@ -268,7 +293,7 @@ __global__ void qk_norm_rope_append_kernel(const void* __restrict__ qkv, int in_
                                            const int* __restrict__ block_table, int bt_stride,
                                            void* __restrict__ k_pages, void* __restrict__ v_pages, int kv_dt,
                                            void* __restrict__ q_out, int q_dt, int n_tok, int n_heads, int n_kv,
-                                           int hd) {
+                                           int hd, int vd, float temp_coef, int temp_every) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per_tok = n_heads + 2 * n_kv;
@@ -276,13 +301,16 @@ __global__ void qk_norm_rope_append_kernel(const void* __restrict__ qkv, int in_
     if (item >= (long)n_tok * per_tok) return;
     const int t = (int)(item / per_tok), h = (int)(item % per_tok);
     const int seq = tok_seq[t];
-    float* x = smem + warp * hd;
-    const size_t in_base = (size_t)t * per_tok * hd + (size_t)h * hd;
     const bool is_q = h < n_heads, is_k = !is_q && h < n_heads + n_kv;
+    const int len = (is_q || is_k) ? hd : vd;
+    const size_t row = (size_t)(n_heads + n_kv) * hd + (size_t)n_kv * vd;
+    float* x = smem + warp * max(hd, vd);
+    const size_t in_base = (size_t)t * row + ((is_q || is_k) ? (size_t)h * hd
+                                                              : (size_t)(n_heads + n_kv) * hd + (size_t)(h - n_heads - n_kv) * vd);
     const void* gamma = is_q ? q_gamma : (is_k ? k_gamma : nullptr);
 
     float ss = 0.0f;
-    for (int i = lane; i < hd; i += 32) {
+    for (int i = lane; i < len; i += 32) {
         const float v = ld_f(qkv, in_base + i, in_dt);
         x[i] = v;
         ss = fmaf(v, v, ss);
@@ -303,8 +331,10 @@ __global__ void qk_norm_rope_append_kernel(const void* __restrict__ qkv, int in_
         __syncwarp();
     }
     if (is_q) {
+        float temp = 1.0f;
+        if (temp_coef != 0.0f) temp = 1.0f + temp_coef * logf((float)((tok_pos[t] + 1) / temp_every) + 1.0f);
         const size_t o = (size_t)t * n_heads * hd + (size_t)h * hd;
-        for (int i = lane; i < hd; i += 32) st_f(q_out, o + i, q_dt, x[i]);
+        for (int i = lane; i < hd; i += 32) st_f(q_out, o + i, q_dt, x[i] * temp);
         return;
     }
     if (seq < 0) return;  // a padded row owns no place in the cache
@@ -312,9 +342,9 @@ __global__ void qk_norm_rope_append_kernel(const void* __restrict__ qkv, int in_
     const int page = block_table[(size_t)seq * bt_stride + pos / kPage];
     if (page < 0) return;
     const int kvh = is_k ? h - n_heads : h - n_heads - n_kv;
-    const size_t o = (((size_t)page * n_kv + kvh) * kPage + pos % kPage) * hd;
+    const size_t o = (((size_t)page * n_kv + kvh) * kPage + pos % kPage) * len;
     void* dst = is_k ? k_pages : v_pages;
-    for (int i = lane; i < hd; i += 32) st_f(dst, o + i, kv_dt, x[i]);
+    for (int i = lane; i < len; i += 32) st_f(dst, o + i, kv_dt, x[i]);
 }
 
 // The bfloat16 run's case: float32 projections in, bfloat16 q and cache out, the whole head rotated,
@@ -387,15 +417,17 @@ extern "C" int nncpu_qk_norm_rope_append(const void* qkv, int in_dt, const void*
                                          int g_dt, float eps, const float* cs, int rot_half, const int* tok_seq,
                                          const int* tok_pos, const int* block_table, int bt_stride, void* k_pages,
                                          void* v_pages, int kv_dt, void* q_out, int q_dt, int n_tok, int n_heads,
-                                         int n_kv, int hd, void* stream) {
-    NN_CHECK(n_tok >= 0 && n_heads > 0 && n_kv >= 0 && hd > 0, "qk_norm_rope_append: sizes");
-    NN_CHECK(hd % 2 == 0 && 2 * rot_half <= hd, "qk_norm_rope_append: head size %d with %d rotated pairs", hd,
+                                         int n_kv, int hd, int vd, float temp_coef, int temp_every, void* stream) {
+    NN_CHECK(n_tok >= 0 && n_heads > 0 && n_kv >= 0 && hd > 0 && vd > 0, "qk_norm_rope_append: sizes");
+    NN_CHECK(vd <= 1024, "qk_norm_rope_append: value size %d is above 1024", vd);
+    NN_CHECK(temp_coef == 0.0f || temp_every > 0, "qk_norm_rope_append: a query temperature every %d positions", temp_every);
+    NN_CHECK((cs == nullptr || hd % 2 == 0) && 2 * rot_half <= hd, "qk_norm_rope_append: head size %d with %d rotated pairs", hd,
              rot_half);
     NN_CHECK((uintptr_t)cs % 8 == 0, "qk_norm_rope_append: the rotation table must be 8-byte aligned (cos/sin pairs)");
     NN_CHECK(hd <= 1024, "qk_norm_rope_append: head size %d is above 1024", hd);
     if (n_tok == 0) return 0;
-    if (in_dt == DT_F32 && q_dt == DT_BF16 && (n_kv == 0 || kv_dt == DT_BF16) && (hd == 64 || hd == 128) &&
-        (cs == nullptr || 2 * rot_half == hd) && (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0) {
+    if (in_dt == DT_F32 && q_dt == DT_BF16 && (n_kv == 0 || kv_dt == DT_BF16) && (hd == 64 || hd == 128) && vd == hd &&
+        temp_coef == 0.0f && (cs == nullptr || 2 * rot_half == hd) && (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0) {
         const long n_items = (long)n_tok * (n_heads + 2 * n_kv);
         const unsigned n_blocks = (unsigned)((n_items + 7) / 8);
         if (hd == 128)
@@ -412,9 +444,10 @@ extern "C" int nncpu_qk_norm_rope_append(const void* qkv, int in_dt, const void*
     const int warps = 4;
     const long items = (long)n_tok * (n_heads + 2 * n_kv);
     const long blocks = (items + warps - 1) / warps;
-    qk_norm_rope_append_kernel<<<(unsigned)blocks, warps * 32, warps * hd * sizeof(float), (cudaStream_t)stream>>>(
+    qk_norm_rope_append_kernel<<<(unsigned)blocks, warps * 32, warps * (hd > vd ? hd : vd) * sizeof(float),
+                                 (cudaStream_t)stream>>>(
         qkv, in_dt, q_gamma, k_gamma, g_dt, eps, (const float2*)cs, rot_half, tok_seq, tok_pos, block_table,
-        bt_stride, k_pages, v_pages, kv_dt, q_out, q_dt, n_tok, n_heads, n_kv, hd);
+        bt_stride, k_pages, v_pages, kv_dt, q_out, q_dt, n_tok, n_heads, n_kv, hd, vd, temp_coef, temp_every);
     NN_LAUNCH_OK("qk_norm_rope_append");
     return 0;
 }
@@ -425,6 +458,8 @@ extern "C" int nncpu_qk_norm_rope_append(const void* qkv, int in_dt, const void*
 // One block per (token, head) walks the span in chunks of 128 keys with an
 // online softmax; the chunk boundaries are fixed by the span alone, so the
 // result does not depend on the batch or on how tokens were cut into steps.
+// Values have vd lanes a head (the output too).  With slope_base != 0 head h
+// takes slope_h * (pos - key) off its scaled scores, slope_h = 2^(-slope_base (h + 1) / n_heads).
 // ---------------------------------------------------------------------------
 constexpr int kAttnThreads = 128;
 
@@ -432,7 +467,7 @@ __global__ void __launch_bounds__(kAttnThreads)
 attention_kernel(const void* __restrict__ q, int q_dt, const void* __restrict__ k_pages,
                  const void* __restrict__ v_pages, int kv_dt, const int* __restrict__ block_table, int bt_stride,
                  const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, void* __restrict__ out,
-                 int out_dt, int n_heads, int n_kv, int hd, float scale, int window) {
+                 int out_dt, int n_heads, int n_kv, int hd, int vd, float scale, int window, float slope_base) {
     extern __shared__ float smem[];
     float* qs = smem;                       // hd
     float* p = smem + hd;                   // kAttnThreads
@@ -441,19 +476,21 @@ attention_kernel(const void* __restrict__ q, int q_dt, const void* __restrict__ 
 
     const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int seq = tok_seq[t];
-    const size_t out_base = (size_t)t * n_heads * hd + (size_t)h * hd;
+    const size_t q_base = (size_t)t * n_heads * hd + (size_t)h * hd;
+    const size_t out_base = (size_t)t * n_heads * vd + (size_t)h * vd;
     if (seq < 0) {
-        for (int d = tid; d < hd; d += kAttnThreads) st_f(out, out_base + d, out_dt, 0.0f);
+        for (int d = tid; d < vd; d += kAttnThreads) st_f(out, out_base + d, out_dt, 0.0f);
         return;
     }
+    const float slope = slope_base != 0.0f ? exp2f(-slope_base * (float)(h + 1) / (float)n_heads) : 0.0f;
     const int pos = tok_pos[t];
     const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
     const int kvh = h / (n_heads / n_kv);
-    for (int d = tid; d < hd; d += kAttnThreads) qs[d] = ld_f(q, out_base + d, q_dt);
+    for (int d = tid; d < hd; d += kAttnThreads) qs[d] = ld_f(q, q_base + d, q_dt);
     __syncthreads();
 
     float m = -INFINITY, l = 0.0f;
-    float acc[8];  // lanes d = tid + 128 * j, hd <= 1024
+    float acc[8];  // lanes d = tid + 128 * j, vd <= 1024
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
 
@@ -463,10 +500,10 @@ attention_kernel(const void* __restrict__ q, int q_dt, const void* __restrict__ 
         long long off = -1;
         if (key <= pos) {
             const int page = block_table[(size_t)seq * bt_stride + key / kPage];
-            off = (((long long)page * n_kv + kvh) * kPage + key % kPage) * hd;
+            off = ((long long)page * n_kv + kvh) * kPage + key % kPage;      // the key's row in its pages
             float dot = 0.0f;
-            for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], ld_f(k_pages, (size_t)off + d, kv_dt), dot);
-            s = dot * scale;
+            for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], ld_f(k_pages, (size_t)off * hd + d, kv_dt), dot);
+            s = dot * scale - slope * (float)(pos - key);
         }
         const float m_new = fmaxf(m, block_max(s, scratch));
         const float w = key <= pos ? expf(s - m_new) : 0.0f;
@@ -480,9 +517,9 @@ attention_kernel(const void* __restrict__ q, int q_dt, const void* __restrict__ 
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int d = tid + kAttnThreads * j;
-            if (d < hd) {
+            if (d < vd) {
                 float a = acc[j] * corr;
-                for (int i = 0; i < n_keys; ++i) a = fmaf(p[i], ld_f(v_pages, (size_t)row[i] + d, kv_dt), a);
+                for (int i = 0; i < n_keys; ++i) a = fmaf(p[i], ld_f(v_pages, (size_t)row[i] * vd + d, kv_dt), a);
                 acc[j] = a;
             }
         }
@@ -492,25 +529,26 @@ attention_kernel(const void* __restrict__ q, int q_dt, const void* __restrict__ 
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const int d = tid + kAttnThreads * j;
-        if (d < hd) st_f(out, out_base + d, out_dt, acc[j] * inv);
+        if (d < vd) st_f(out, out_base + d, out_dt, acc[j] * inv);
     }
 }
 
 extern "C" int nncpu_attention(const void* q, int q_dt, const void* k_pages, const void* v_pages, int kv_dt,
                                const int* block_table, int bt_stride, const int* tok_seq, const int* tok_pos,
-                               void* out, int out_dt, int n_tok, int n_heads, int n_kv, int hd, float scale,
-                               int window, void* stream) {
+                               void* out, int out_dt, int n_tok, int n_heads, int n_kv, int hd, int vd, float scale,
+                               int window, float slope_base, void* stream) {
     NN_CHECK(n_tok >= 0 && n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0,
              "attention: %d heads over %d key/value heads", n_heads, n_kv);
-    NN_CHECK(hd > 0 && hd <= 1024 && hd % 2 == 0, "attention: head size %d must be even and at most 1024", hd);
+    NN_CHECK(hd > 0 && hd <= 1024, "attention: head size %d must be positive and at most 1024", hd);
+    NN_CHECK(vd > 0 && vd <= 1024, "attention: value size %d must be positive and at most 1024", vd);
     NN_CHECK(window >= 0, "attention: window %d", window);
     if (n_tok == 0) return 0;
     const size_t smem = (hd + kAttnThreads) * sizeof(float) + kAttnThreads * sizeof(long long) + 8;
     dim3 grid(n_tok, n_heads);
     attention_kernel<<<grid, kAttnThreads, smem, (cudaStream_t)stream>>>(q, q_dt, k_pages, v_pages, kv_dt,
                                                                          block_table, bt_stride, tok_seq, tok_pos,
-                                                                         out, out_dt, n_heads, n_kv, hd, scale,
-                                                                         window);
+                                                                         out, out_dt, n_heads, n_kv, hd, vd, scale,
+                                                                         window, slope_base);
     NN_LAUNCH_OK("attention");
     return 0;
 }
@@ -536,6 +574,50 @@ extern "C" int nncpu_swiglu(const void* gu, int in_dt, void* out, int out_dt, in
     swiglu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gu, in_dt, out, out_dt, n_tok,
                                                                                       inter);
     NN_LAUNCH_OK("swiglu");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// xIELU, an activation with two learned numbers (p, q) = params[0..1]:
+//   z > 0:  softplus(p) z^2 + z / 2
+//   z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2
+// softplus and the activation are computed in 32-bit whatever the tensors hold.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
+
+__global__ void xielu_kernel(const void* __restrict__ x, int in_dt, const void* __restrict__ params, int p_dt,
+                             void* __restrict__ out, int out_dt, long n) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const float a_pos = softplus_f(ld_f(params, 0, p_dt));
+    const float a_neg = 0.5f + softplus_f(ld_f(params, 1, p_dt));
+    const float z = ld_f(x, (size_t)idx, in_dt);
+    const float y = z > 0.0f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);
+    st_f(out, (size_t)idx, out_dt, y);
+}
+
+extern "C" int nncpu_xielu(const void* x, int in_dt, const void* params, int p_dt, void* out, int out_dt, long n,
+                           void* stream) {
+    NN_CHECK(n >= 0 && params != nullptr, "xielu: %ld elements", n);
+    if (n == 0) return 0;
+    xielu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, in_dt, params, p_dt, out, out_dt, n);
+    NN_LAUNCH_OK("xielu");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Soft cap in place: x <- cap * tanh(x / cap), float32.
+// ---------------------------------------------------------------------------
+__global__ void softcap_kernel(float* __restrict__ x, long n, float cap) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < n) x[idx] = cap * tanhf(x[idx] / cap);
+}
+
+extern "C" int nncpu_softcap(float* x, long n, float cap, void* stream) {
+    NN_CHECK(n >= 0 && cap > 0.0f, "softcap: %ld elements, cap %g", n, cap);
+    if (n == 0) return 0;
+    softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, n, cap);
+    NN_LAUNCH_OK("softcap");
     return 0;
 }
 

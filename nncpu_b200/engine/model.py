@@ -64,12 +64,14 @@ def build_blocks(spec: ModelSpec) -> list:
 def parameter_list(spec: ModelSpec) -> List[ParamSpec]:
     """Every tensor the model of ``spec`` reads from its file."""
     e, o = spec.embedding, spec.output
-    params = [ParamSpec(f"{e.name}.weight", (e.vocab_size, e.hidden_size))]
+    params = [ParamSpec(e.name + e.suffix, (e.vocab_size, e.hidden_size))]
+    if e.positions is not None:
+        params.append(ParamSpec(e.positions, (e.n_positions, e.hidden_size)))
     for block in build_blocks(spec):
         params += block.params()
     params += build("norm", o.norm).params()
     if not o.tied:
-        params.append(ParamSpec(f"{o.name}.weight", (o.vocab_size, o.hidden_size)))
+        params.append(ParamSpec(o.name + o.suffix, (o.vocab_size, o.hidden_size)))
     return params
 
 
@@ -81,10 +83,13 @@ class Model:
         self.spec = spec = config.model_spec()
         self.rt = rt
         self.blocks = build_blocks(spec)
+        self.n_parameters = sum(t.numel() for t in tensors.values())
         self.final_norm = build("norm", spec.output.norm)
         # `tensors` is consumed: parts take what they fuse out of it, so that no second copy stays alive
-        self.embed_table = tensors[f"{spec.embedding.name}.weight"]
-        self.lm_head = self.embed_table if spec.output.tied else tensors[f"{spec.output.name}.weight"]
+        self.embed_table = tensors[spec.embedding.name + spec.embedding.suffix]
+        # learned position vectors, added to the embedding rows: sequences cannot grow beyond the table
+        self.pos_table = None if spec.embedding.positions is None else tensors[spec.embedding.positions]
+        self.lm_head = self.embed_table if spec.output.tied else tensors[spec.output.name + spec.output.suffix]
         for block in self.blocks:
             block.bind(tensors, rt)
         self.final_norm.bind(tensors, rt)
@@ -149,8 +154,8 @@ class Model:
     def info(self) -> dict:
         """What the model is, in the reference's terms (crates/nncpu/src/lib.rs:150-190): sizes, counts and the
         bytes its weights hold on the device.  Head counts are those of the first mixer that has heads."""
-        n_params = sum(int(torch.tensor(p.shape).prod()) for p in parameter_list(self.spec) if p.required)
-        heads = next((b.mixer for b in self.spec.layers if hasattr(b.mixer, "n_heads")), None)
+        n_params = self.n_parameters
+        heads = next((b.mixer for b in self.spec.layers if hasattr(b.mixer, "n_kv_heads")), None)
         weights = self.weight_bytes_per_step() + (0 if self.spec.output.tied else
                                                   self.embed_table.numel() * self.embed_table.element_size())
         return {"architecture": self.spec.architecture, "dtype": str(self.rt.dtype).replace("torch.", ""),
@@ -168,7 +173,7 @@ class Model:
         rt, spec = self.rt, self.spec
         residual = rt.empty(ctx.n_tokens, spec.hidden_size, dtype=torch.float32)
         with rt.phase("embed"):
-            ops.embed(self.embed_table, ctx.tok_ids, residual, spec.embedding.scale)
+            ops.embed(self.embed_table, ctx.tok_ids, residual, spec.embedding.scale, self.pos_table, ctx.tok_pos)
         ctx.next_norm = ctx.after_block = None
         fusing = rt.dtype == torch.bfloat16 and rt.fuses_norms(ctx.n_tokens, spec.hidden_size)
         if fusing:
@@ -187,4 +192,6 @@ class Model:
         logits = rt.empty(ctx.n_wanted, spec.vocab_size, dtype=torch.float32)
         with rt.phase("lm_head", self.lm_head, ctx.n_wanted):
             rt.linear(x, self.lm_head, None, logits)
+            if spec.output.softcap > 0.0:
+                ops.softcap(logits, spec.output.softcap)
         return logits

@@ -184,6 +184,9 @@ class Engine:
         # A sequence may grow as long as the cache lets it.  The model's own position range only sets a
         # session's default context, as in the reference (crates/nncpu/src/session/engine.rs:113-117): rotary
         # positions need no table, so nothing breaks beyond it.
+        # A table of learned position vectors is the exception: a sequence cannot outgrow it.
+        if model.pos_table is not None:
+            max_seq_len = min(max_seq_len or model.pos_table.shape[0], model.pos_table.shape[0])
         self.cache = Cache(requests, cache_of, max_tokens, kv_dtype or rt.dtype, rt.device, n_slots=n_slots,
                            max_seq_len=max_seq_len)
         self.vocab_size = model.spec.vocab_size

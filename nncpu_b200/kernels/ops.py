@@ -121,22 +121,29 @@ def _f(v) -> ctypes.c_float:
     return ctypes.c_float(float(v))
 
 
-def embed(table, ids, out, scale: float = 1.0) -> None:
-    """out[t] = table[ids[t]] * scale; out is float32 [n, hidden]; ids int32."""
+def embed(table, ids, out, scale: float = 1.0, pos_table=None, positions=None) -> None:
+    """out[t] = table[ids[t]] * scale; out is float32 [n, hidden]; ids int32.  With ``pos_table`` [n_pos, hidden]
+    (learned position vectors) and ``positions`` int32 [n]: out[t] += pos_table[positions[t]], not scaled."""
     n, hidden = out.shape
     assert out.dtype == torch.float32 and ids.dtype == torch.int32 and ids.numel() >= n
+    n_pos = 0
+    if pos_table is not None:
+        n_pos = pos_table.shape[0]
+        assert pos_table.shape[1] == hidden and positions.dtype == torch.int32 and positions.numel() >= n
     _call("generic", "nncpu_embed", _ptr(table), _i(_code(table)), _ptr(ids), _ptr(out), _i(n), _i(hidden),
-          _i(table.shape[0]), _f(scale), _stream())
+          _i(table.shape[0]), _f(scale), _ptr(pos_table), _i(_code(pos_table)),
+          _ptr(positions if pos_table is not None else None), _i(n_pos), _stream())
 
 
-def rmsnorm(x, gamma, eps: float, out, rows=None) -> None:
-    """out[r] = rmsnorm(x[rows[r]] or x[r]) * gamma over the last axis."""
+def rmsnorm(x, gamma, eps: float, out, rows=None, gamma_offset: float = 0.0, accumulate: bool = False) -> None:
+    """out[r] = rmsnorm(x[rows[r]] or x[r]) * (gamma + gamma_offset) over the last axis; with ``accumulate``
+    the result is added to ``out`` (the norm that closes a sublayer adds into the residual stream)."""
     dim = x.shape[-1]
     n_rows = out.numel() // dim
     assert gamma is None or gamma.numel() == dim
     assert rows is None or (rows.dtype == torch.int32 and rows.numel() >= n_rows)
     _call("generic", "nncpu_rmsnorm", _ptr(x), _i(_code(x)), _ptr(gamma), _i(_code(gamma)), _ptr(out),
-          _i(_code(out)), _ptr(rows), _i(n_rows), _i(dim), _f(eps), _stream())
+          _i(_code(out)), _ptr(rows), _i(n_rows), _i(dim), _f(eps), _f(gamma_offset), _i(accumulate), _stream())
 
 
 def linear_simt(x, w, bias, out, accumulate: bool = False) -> None:
@@ -320,30 +327,37 @@ def rope_table(positions, inv_freq, out, position_scale: float = 1.0, by_pair: b
 
 
 def qk_norm_rope_append(qkv, q_gamma, k_gamma, eps, cos_sin, tok_seq, tok_pos, block_table, k_pages, v_pages,
-                        q_out, n_heads: int, n_kv: int, head_dim: int) -> None:
+                        q_out, n_heads: int, n_kv: int, head_dim: int, v_head_dim: int = 0, q_temp=None) -> None:
     """Per-head norm and rotation of q and k, and the append of k and v to
-    their pages.  ``n_kv`` 0: qkv holds q only and nothing is appended."""
+    their pages.  ``n_kv`` 0: qkv holds q only and nothing is appended.  ``v_head_dim``: lanes of a value
+    head when they differ from ``head_dim``.  ``q_temp = (coef, every)``: the query at position p is
+    multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)."""
     n = q_out.shape[0]
     rot_half = 0 if cos_sin is None else cos_sin.shape[1]
-    assert qkv.shape == (n, (n_heads + 2 * n_kv) * head_dim) and q_out.shape == (n, n_heads * head_dim)
+    v_head_dim = v_head_dim or head_dim
+    coef, every = q_temp if q_temp is not None else (0.0, 1)
+    assert qkv.shape == (n, (n_heads + n_kv) * head_dim + n_kv * v_head_dim) and q_out.shape == (n, n_heads * head_dim)
     assert q_gamma is None or k_gamma is None or q_gamma.dtype == k_gamma.dtype
     g = q_gamma if q_gamma is not None else k_gamma
     bt_stride = block_table.shape[1] if block_table is not None else 0
     _call("generic", "nncpu_qk_norm_rope_append", _ptr(qkv), _i(_code(qkv)), _ptr(q_gamma), _ptr(k_gamma),
           _i(_code(g)), _f(eps), _ptr(cos_sin), _i(rot_half), _ptr(tok_seq), _ptr(tok_pos), _ptr(block_table),
           _i(bt_stride), _ptr(k_pages), _ptr(v_pages), _i(_code(k_pages)), _ptr(q_out), _i(_code(q_out)), _i(n),
-          _i(n_heads), _i(n_kv), _i(head_dim), _stream())
+          _i(n_heads), _i(n_kv), _i(head_dim), _i(v_head_dim), _f(coef), _i(every), _stream())
 
 
 def attention(q, k_pages, v_pages, block_table, tok_seq, tok_pos, out, n_heads: int, n_kv: int, head_dim: int,
-              scale: float, window: int = 0) -> None:
-    """Causal attention of each token over its sequence's pages."""
+              scale: float, window: int = 0, v_head_dim: int = 0, slope_base: float = 0.0) -> None:
+    """Causal attention of each token over its sequence's pages.  ``v_head_dim``: lanes of a value head (and of
+    the output) when they differ from ``head_dim``.  ``slope_base`` b != 0: head h takes
+    2^(-b (h + 1) / n_heads) * (query position - key position) off its scaled scores."""
     n = q.shape[0]
-    assert q.shape == (n, n_heads * head_dim) and out.shape == q.shape
+    v_head_dim = v_head_dim or head_dim
+    assert q.shape == (n, n_heads * head_dim) and out.shape == (n, n_heads * v_head_dim)
     assert k_pages.dtype == v_pages.dtype and block_table.dtype == torch.int32
     _call("generic", "nncpu_attention", _ptr(q), _i(_code(q)), _ptr(k_pages), _ptr(v_pages), _i(_code(k_pages)),
           _ptr(block_table), _i(block_table.shape[1]), _ptr(tok_seq), _ptr(tok_pos), _ptr(out), _i(_code(out)),
-          _i(n), _i(n_heads), _i(n_kv), _i(head_dim), _f(scale), _i(window), _stream())
+          _i(n), _i(n_heads), _i(n_kv), _i(head_dim), _i(v_head_dim), _f(scale), _i(window), _f(slope_base), _stream())
 
 
 def attention_mma_supported(n_heads: int, n_kv: int, head_dim: int, *tensors) -> bool:
@@ -449,6 +463,44 @@ def swiglu(gate_up, out) -> None:
     assert gate_up.shape == (n, 2 * inter)
     _call("generic", "nncpu_swiglu", _ptr(gate_up), _i(_code(gate_up)), _ptr(out), _i(_code(out)), _i(n),
           _i(inter), _stream())
+
+
+def xielu(x, params, out) -> None:
+    """out = xIELU(x) elementwise with the two learned numbers ``params`` = (p, q): for z > 0
+    softplus(p) z^2 + z/2, else (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2; computed in 32-bit."""
+    assert x.shape == out.shape and params.numel() == 2 and x.is_contiguous() and out.is_contiguous()
+    _call("generic", "nncpu_xielu", _ptr(x), _i(_code(x)), _ptr(params), _i(_code(params)), _ptr(out), _i(_code(out)),
+          ctypes.c_long(x.numel()), _stream())
+
+
+def softcap(x, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place; x float32."""
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _call("generic", "nncpu_softcap", _ptr(x), ctypes.c_long(x.numel()), _f(cap), _stream())
+
+
+def gla_scan(proj, z, state, seq_slots, cu_seqlens, o, n_seqs: int, n_heads: int, d: int, e: int, q_scale: float,
+             tau: float) -> None:
+    """Gated linear attention's recurrence over the step's tokens, sequence by sequence in order.  ``proj``
+    float32 [n, 2 H d + 2 H e] holds q, k, v and the output gate per token, ``z`` float32 [n, H d] the decay
+    logits; ``state`` float32 [slots, H, d, e] is read and left updated for the slots in ``seq_slots`` (a negative
+    slot: a padding sequence, zeros out); ``o`` float32 [n, H e] receives S_t^T q_t."""
+    n = o.shape[0]
+    assert proj.dtype == z.dtype == state.dtype == o.dtype == torch.float32
+    assert proj.shape == (n, 2 * n_heads * (d + e)) and z.shape == (n, n_heads * d) and o.shape == (n, n_heads * e)
+    assert state.shape[1:] == (n_heads, d, e) and state.is_contiguous() and proj.is_contiguous()
+    assert seq_slots.dtype == torch.int32 and cu_seqlens.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1
+    _call("recurrent", "nncpu_gla_scan", _ptr(proj), _i(proj.shape[1]), _ptr(z), _ptr(state), _ptr(seq_slots),
+          _ptr(cu_seqlens), _ptr(o), _i(n_seqs), _i(n_heads), _i(d), _i(e), _f(q_scale), _f(tau), _stream())
+
+
+def gla_output(o, proj, weight, eps: float, out, n_heads: int, d: int, e: int) -> None:
+    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * silu(g[t, h]) with g the last H e lanes of ``proj``'s rows."""
+    n = o.shape[0]
+    assert o.dtype == proj.dtype == torch.float32 and o.shape == (n, n_heads * e) and out.shape == o.shape
+    assert weight.numel() == e
+    _call("recurrent", "nncpu_gla_output", _ptr(o), _ptr(proj), _i(proj.shape[1]), _i(2 * n_heads * d + n_heads * e),
+          _ptr(weight), _i(_code(weight)), _f(eps), _ptr(out), _i(_code(out)), _i(n), _i(n_heads), _i(e), _stream())
 
 
 def gather_rows(x, rows, out) -> None:

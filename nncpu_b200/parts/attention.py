@@ -7,6 +7,11 @@ residual stream (crates/nncpu/src/model/forward.rs:197-439).
 q, k and v projections are stored as one matrix so the input is read once.
 An entry that reads another entry's cache has no k/v projection at all
 (crates/nncpu/src/model/forward.rs:210,240-255).
+
+Options a spec may switch on: value heads of another size than the query/key heads (``v_head_dim``), a
+distance bias per head (``slope_base`` b: head h of H takes 2^(-b (h + 1) / H) * (i - j) off the scaled score
+of query i and key j), and a query temperature (the query at position p times
+1 + coef * ln(floor((p + 1) / every) + 1)).  Scores, bias and softmax are 32-bit.
 """
 from __future__ import annotations
 
@@ -32,27 +37,43 @@ class Attention(Mixer):
             raise UnsupportedModel(f"{s.name}: {s.n_heads} heads over {s.n_kv_heads} key/value heads")
         if s.qk_norm is not None and s.qk_norm.kind != "rmsnorm":
             raise UnsupportedModel(f"{s.name}: per-head norm of kind {s.qk_norm.kind!r} is not supported")
+        if s.tensor_names not in ("proj", "short"):
+            raise UnsupportedModel(f"{s.name}: tensor names of style {s.tensor_names!r}")
+        self.v_dim = s.v_head_dim or s.head_dim
         self.q_size = s.n_heads * s.head_dim
         self.kv_size = 0 if reads_other_cache else s.n_kv_heads * s.head_dim
+        self.v_size = 0 if reads_other_cache else s.n_kv_heads * self.v_dim
+        self.out_size = s.n_heads * self.v_dim
+        # what the tensor-core attention kernels and the fused epilogues do not know: they are left to the 32-bit kernel
+        self.plain_core = self.v_dim != s.head_dim or s.slope_base != 0.0 or s.q_temp_coef != 0.0
+        self.q_temp = (s.q_temp_coef, s.q_temp_every) if s.q_temp_coef != 0.0 else None
         self.position = None if s.position is None else base.build("position", s.position)
 
     def kv_request(self):
         s = self.spec
-        return None if self.shared_kv else KVRequest(s.n_kv_heads, s.head_dim, s.window)
+        return None if self.shared_kv else KVRequest(s.n_kv_heads, s.head_dim, s.window,
+                                                     0 if self.v_dim == s.head_dim else self.v_dim)
 
     def _proj_names(self):
         return ["q_proj"] if self.shared_kv else ["q_proj", "k_proj", "v_proj"]
 
+    def _tensor(self, proj: str, bias: bool = False) -> str:
+        """The file's name of a projection's matrix or bias."""
+        s = self.spec
+        if s.tensor_names == "short":
+            return f"{s.name}.{proj[0]}" + (".b" if bias else "")
+        return f"{s.name}.{proj}." + ("bias" if bias else "weight")
+
     def params(self):
         s, p = self.spec, []
-        sizes = {"q_proj": self.q_size, "k_proj": self.kv_size, "v_proj": self.kv_size}
+        sizes = {"q_proj": self.q_size, "k_proj": self.kv_size, "v_proj": self.v_size}
         for n in self._proj_names():
-            p.append(ParamSpec(f"{s.name}.{n}.weight", (sizes[n], s.hidden_size)))
+            p.append(ParamSpec(self._tensor(n), (sizes[n], s.hidden_size)))
             if s.qkv_bias:
-                p.append(ParamSpec(f"{s.name}.{n}.bias", (sizes[n],)))
-        p.append(ParamSpec(f"{s.name}.o_proj.weight", (s.hidden_size, self.q_size)))
+                p.append(ParamSpec(self._tensor(n, bias=True), (sizes[n],)))
+        p.append(ParamSpec(self._tensor("o_proj"), (s.hidden_size, self.out_size)))
         if s.out_bias_optional:
-            p.append(ParamSpec(f"{s.name}.o_proj.bias", (s.hidden_size,), required=False))
+            p.append(ParamSpec(self._tensor("o_proj", bias=True), (s.hidden_size,), required=False))
         if s.qk_norm is not None:
             p.append(ParamSpec(f"{s.qk_norm.name}.q_norm.weight", (s.head_dim,), init=("one_plus_normal", 0.1)))
             if not self.shared_kv:
@@ -62,15 +83,15 @@ class Attention(Mixer):
     def bind(self, tensors, rt):
         s, self.rt = self.spec, rt
         names = self._proj_names()
-        ws = [tensors.pop(f"{s.name}.{n}.weight") for n in names]
+        ws = [tensors.pop(self._tensor(n)) for n in names]
         self.w_qkv = ws[0] if len(ws) == 1 else torch.cat(ws, dim=0).contiguous()
         del ws
         self.b_qkv = None
         if s.qkv_bias:
-            bs = [tensors.pop(f"{s.name}.{n}.bias") for n in names]
+            bs = [tensors.pop(self._tensor(n, bias=True)) for n in names]
             self.b_qkv = bs[0] if len(bs) == 1 else torch.cat(bs, dim=0).contiguous()
-        self.w_o = tensors[f"{s.name}.o_proj.weight"]
-        self.b_o = tensors.get(f"{s.name}.o_proj.bias")
+        self.w_o = tensors[self._tensor("o_proj")]
+        self.b_o = tensors.get(self._tensor("o_proj", bias=True))
         self.q_gamma = self.k_gamma = None
         if s.qk_norm is not None:
             self.q_gamma = tensors[f"{s.qk_norm.name}.q_norm.weight"]
@@ -85,7 +106,7 @@ class Attention(Mixer):
         s, rt = self.spec, self.rt
         n = x.shape[0]
         eps = s.qk_norm.eps if s.qk_norm else 0.0
-        attn = rt.empty(n, self.q_size)
+        attn = rt.empty(n, self.out_size)
         if self._fused_qkv(x, cache):
             # a prompt: norm, rotation and the cache append happen in the projection's epilogue, on its
             # float32 accumulators; its threads are tokens, so the rotation table is laid out by pair
@@ -103,7 +124,7 @@ class Attention(Mixer):
                 self._attend(ctx, q, cache, attn)
         else:
             # the projections stay in float32 until the per-head norm and the rotation have been applied
-            qkv = rt.empty(n, self.q_size + 2 * self.kv_size, dtype=torch.float32)
+            qkv = rt.empty(n, self.q_size + self.kv_size + self.v_size, dtype=torch.float32)
             with rt.phase("attn_qkv", self.w_qkv, n):
                 rt.linear(x, self.w_qkv, self.b_qkv, qkv)
             with rt.phase("attn_rope"):
@@ -121,7 +142,7 @@ class Attention(Mixer):
                 with rt.phase("attn_rope"):
                     ops.qk_norm_rope_append(qkv, self.q_gamma, self.k_gamma, eps, cos_sin, ctx.tok_seq, ctx.tok_pos,
                                             cache.block_table, cache.k_pages, cache.v_pages, q, s.n_heads,
-                                            0 if self.shared_kv else s.n_kv_heads, s.head_dim)
+                                            0 if self.shared_kv else s.n_kv_heads, s.head_dim, self.v_dim, self.q_temp)
                 with self._core_phase(ctx, cache):
                     self._attend(ctx, q, cache, attn)
         with rt.phase("attn_out", self.w_o, n):
@@ -135,14 +156,14 @@ class Attention(Mixer):
             return perf._NULL
         s = self.spec
         keys = ctx.span_sum(s.window)
-        return self.rt.phase("attn_core", nbytes=2.0 * keys * s.n_kv_heads * s.head_dim * cache.k_pages.element_size(),
-                             flops=4.0 * keys * self.q_size)
+        return self.rt.phase("attn_core", nbytes=1.0 * keys * s.n_kv_heads * (s.head_dim + self.v_dim) * cache.k_pages.element_size(),
+                             flops=2.0 * keys * (self.q_size + self.out_size))
 
     def _decode_from_projections(self, ctx, cache) -> bool:
         """Whether this step's attention can start from the float32 projections: a decode step on the tensor-core
         kernel, every lane of a head rotated (or none), norm weights of one type."""
         s = self.spec
-        return (ctx.is_decode and self.rt.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
+        return (not self.plain_core and ctx.is_decode and self.rt.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
                 and ops.attention_mma_supported(s.n_heads, s.n_kv_heads, s.head_dim)
                 and (self.position is None or self.position.half * 2 == s.head_dim)
                 and (self.q_gamma is None or self.k_gamma is None or self.q_gamma.dtype == self.k_gamma.dtype))
@@ -161,7 +182,7 @@ class Attention(Mixer):
         s = self.spec
         if isinstance(x, base.DeferredNorm):
             x = x.x_gamma
-        return (not self.shared_kv and self.b_qkv is None and x.dtype == torch.bfloat16
+        return (not self.plain_core and not self.shared_kv and self.b_qkv is None and x.dtype == torch.bfloat16
                 and self.w_qkv.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
                 and (self.position is None or (self.position.tables_by_pair and self.position.half * 2 == s.head_dim))
                 and ops.linear_tc_qkv_supported(x, s.n_heads, s.n_kv_heads, s.head_dim))
@@ -171,9 +192,9 @@ class Attention(Mixer):
         decode, tcgen05 prefill for prompts, mma.sync prefill for a few tokens
         per sequence; everything else: the 32-bit kernel."""
         s = self.spec
-        if not ops.attention_mma_supported(s.n_heads, s.n_kv_heads, s.head_dim, q, cache.k_pages, attn):
+        if self.plain_core or not ops.attention_mma_supported(s.n_heads, s.n_kv_heads, s.head_dim, q, cache.k_pages, attn):
             ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos, attn,
-                          s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window)
+                          s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, self.v_dim, s.slope_base)
         elif ctx.is_decode:
             n_splits, scratch = self._decode_splits(ctx)
             ops.attention_decode_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos,

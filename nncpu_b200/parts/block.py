@@ -62,3 +62,56 @@ class PreNormBlock(Block):
             ctx.next_norm = after
             self.feed_forward.forward(ctx, x, residual)
         # ctx.next_norm stays: the block that follows finds its request there, fulfilled or not
+
+
+@register_block("sandwich")
+class SandwichBlock(Block):
+    """A norm before and after each sublayer: x += norm1_post(mixer(norm1(x))), then, if the layer has a
+    feed-forward, x += norm2_post(feed_forward(norm2(x))).  A sublayer writes its output into a float32 branch
+    of its own (the parts add into what they are given, so the branch starts at zero), and the closing norm adds
+    its result into the residual stream."""
+
+    def __init__(self, spec, reads_other_cache: bool = False):
+        kwargs = {"reads_other_cache": True} if reads_other_cache else {}
+        self.norm1 = base.build("norm", spec.norm1)
+        self.mixer = base.build("mixer", spec.mixer, **kwargs)
+        self.norm1_post = base.build("norm", spec.norm1_post)
+        self.feed_forward = None if spec.feed_forward is None else base.build("feed_forward", spec.feed_forward)
+        self.norm2 = self.norm2_post = None
+        if self.feed_forward is not None:
+            self.norm2 = base.build("norm", spec.norm2)
+            self.norm2_post = base.build("norm", spec.norm2_post)
+        self._parts = tuple(p for p in (self.norm1, self.mixer, self.norm1_post, self.norm2, self.feed_forward,
+                                        self.norm2_post) if p is not None)
+
+    def params(self):
+        return [p for part in self._parts for p in part.params()]
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        for part in self._parts:
+            part.bind(tensors, rt)
+
+    def weight_bytes(self):
+        return sum(part.weight_bytes() for part in self._parts)
+
+    def cache_requests(self):
+        return [(self.mixer.kv_request(), self.mixer.state_request())]
+
+    def _sublayer(self, ctx, norm, run, norm_post, residual):
+        rt = self.rt
+        with rt.scope():
+            x = norm.forward(ctx, residual)
+            branch = rt.empty(*residual.shape, dtype=residual.dtype)
+            if not branch.is_meta:
+                branch.zero_()
+            run(x, branch)
+            norm_post.add_into(ctx, branch, residual)
+
+    def forward(self, ctx, residual, caches):
+        ctx.next_norm = ctx.after_block = None      # these norms do not ride on the products around them
+        self._sublayer(ctx, self.norm1, lambda x, out: self.mixer.forward(ctx, x, out, caches[0]), self.norm1_post,
+                       residual)
+        if self.feed_forward is not None:
+            self._sublayer(ctx, self.norm2, lambda x, out: self.feed_forward.forward(ctx, x, out), self.norm2_post,
+                           residual)

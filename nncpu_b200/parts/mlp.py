@@ -1,7 +1,8 @@
-"""Gated feed-forward: down(act(gate(x)) * up(x)) with act = SiLU
+"""Feed-forwards.  Gated: down(act(gate(x)) * up(x)) with act = SiLU
 (crates/nncpu/src/model/forward.rs:763-782,
 crates/nncpu/src/kernels/scalar.rs:146-150).  gate and up are stored as one
 matrix so the input is read once; the result is added to the residual stream.
+Dense: down(act(up(x) + b_up)) + b_down with act = xIELU, an activation with two learned numbers.
 """
 from __future__ import annotations
 
@@ -62,3 +63,44 @@ class GatedMlp(FeedForward):
         with rt.phase("ffn_down", self.w_down, n):
             # the last write into the residual stream: it may leave the next norm its input
             rt.linear(act, self.w_down, None, residual, accumulate=True, then_norm=getattr(ctx, "next_norm", None))
+
+
+@register_feed_forward("dense_mlp")
+class DenseMlp(FeedForward):
+    """down(xielu(up(x) + b_up)) + b_down.  The up product's result stays in float32 and the activation
+    (softplus of its two numbers included) is computed in 32-bit; its output is rounded to the run's element type
+    for the down product.  Tensors: ``<name>.up``, ``.up.b``, ``.down``, ``.down.b``, ``.act`` (p, q)."""
+
+    def __init__(self, spec):
+        if spec.activation != "xielu":
+            raise UnsupportedModel(f"{spec.name}: activation {spec.activation!r} is not supported (supported: xielu)")
+        self.spec = spec
+
+    def params(self):
+        s = self.spec
+        return [ParamSpec(f"{s.name}.up", (s.intermediate_size, s.hidden_size)),
+                ParamSpec(f"{s.name}.up.b", (s.intermediate_size,)),
+                ParamSpec(f"{s.name}.down", (s.hidden_size, s.intermediate_size)),
+                ParamSpec(f"{s.name}.down.b", (s.hidden_size,)),
+                ParamSpec(f"{s.name}.act", (2,), init=("normal", 0.5))]
+
+    def bind(self, tensors, rt):
+        s, self.rt = self.spec, rt
+        self.w_up, self.b_up = tensors[f"{s.name}.up"], tensors[f"{s.name}.up.b"]
+        self.w_down, self.b_down = tensors[f"{s.name}.down"], tensors[f"{s.name}.down.b"]
+        self.act = tensors[f"{s.name}.act"]
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down))
+
+    def forward(self, ctx, x, residual):
+        s, rt = self.spec, self.rt
+        n = x.shape[0]
+        up = rt.empty(n, s.intermediate_size, dtype=torch.float32)
+        with rt.phase("ffn_up", self.w_up, n):
+            rt.linear(x, self.w_up, self.b_up, up)
+        act = rt.empty(n, s.intermediate_size)
+        with rt.phase("ffn_act"):
+            ops.xielu(up, self.act, act)
+        with rt.phase("ffn_down", self.w_down, n):
+            rt.linear(act, self.w_down, self.b_down, residual, accumulate=True)

@@ -37,8 +37,10 @@ def check_tensors(file_shapes: Dict[str, tuple], params: Iterable[ParamSpec], wh
     wanted = {p.name: p for p in params}
     missing = sorted(n for n, p in wanted.items() if p.required and n not in file_shapes)
     unexpected = sorted(n for n in file_shapes if n not in wanted)
+    def fits(have, want) -> bool:       # an axis a part gave as -1 is the file's to decide
+        return len(have) == len(want) and all(w == -1 or h == w for h, w in zip(have, want))
     wrong = sorted((n, tuple(file_shapes[n]), tuple(p.shape)) for n, p in wanted.items()
-                   if n in file_shapes and tuple(file_shapes[n]) != tuple(p.shape))
+                   if n in file_shapes and not fits(tuple(file_shapes[n]), tuple(p.shape)))
     if not (missing or unexpected or wrong):
         return
     lines = [f"{where} does not hold the tensors this model needs:"]
