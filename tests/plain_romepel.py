@@ -95,6 +95,18 @@ def query_temperature(p, coef, every):
 
 # -- mixers -------------------------------------------------------------------------------
 
+def gla_recurrence(q, k, v, alpha, S):
+    """S_t = diag(alpha_t) S_(t-1) + k_t v_t^T and o_t = S_t^T q_t, head by head and token by token.
+    q, k, alpha [T, H, d]; v [T, H, e]; S [H, d, e] is updated in place.  Returns o [T, H, e]."""
+    T, H = q.shape[:2]
+    out = np.zeros((T, H, v.shape[2]))
+    for t in range(T):
+        for hd in range(H):
+            S[hd] = alpha[t, hd][:, None] * S[hd] + np.outer(k[t, hd], v[t, hd])
+            out[t, hd] = S[hd].T @ q[t, hd]
+    return out
+
+
 def gla_mixer(h, w, name, m, state=None):
     """Gated linear attention over the rows of h (one sequence, in order).  ``state`` [H, d, e] is what earlier
     rows left (None: zeros); returns (output rows, state after the last row)."""
@@ -109,14 +121,30 @@ def gla_mixer(h, w, name, m, state=None):
     q, k, alpha = (a.reshape(T, H, d) for a in (q, k, alpha))
     v = v.reshape(T, H, e)
     S = np.zeros((H, d, e)) if state is None else np.array(state, dtype=np.float64)
-    out = np.zeros((T, H, e))
-    for t in range(T):
-        for hd in range(H):
-            S[hd] = alpha[t, hd][:, None] * S[hd] + np.outer(k[t, hd], v[t, hd])
-            out[t, hd] = S[hd].T @ q[t, hd]
+    out = gla_recurrence(q, k, v, alpha, S)
     out = rms(out, m["_eps"]) * w[f"{name}.norm"]          # per head over e, one weight shared by the heads
     out = out.reshape(T, H * e) * silu(g)
     return out @ w[f"{name}.o"].T, S
+
+
+def biased_attention(q, k, v, pos, scale, window, slopes):
+    """Softmax attention of queries at positions ``pos`` over keys 0 .. N-1: query i sees key j when
+    0 <= i - j (< window, if there is one); head h takes slopes[h] * (i - j) off the scaled score.
+    q [T, H, d]; k [N, G, d]; v [N, G, e].  Returns [T, H, e]."""
+    T, H = q.shape[:2]
+    G = k.shape[1]
+    dist = np.asarray(pos)[:, None] - np.arange(k.shape[0])[None, :]      # i - j
+    seen = (dist >= 0) & ((dist < window) if window else True)
+    out = np.zeros((T, H, v.shape[2]))
+    for hd in range(H):
+        kv = hd // (H // G)
+        s = (q[:, hd] @ k[:, kv].T) * scale - slopes[hd] * dist
+        s = np.where(seen, s, -np.inf)
+        s = s - s.max(axis=1, keepdims=True)
+        p = np.exp(s)
+        p /= p.sum(axis=1, keepdims=True)
+        out[:, hd] = p @ v[:, kv]
+    return out
 
 
 def attention_mixer(h, w, name, m, first_pos=0, past_k=None, past_v=None):
@@ -136,20 +164,8 @@ def attention_mixer(h, w, name, m, first_pos=0, past_k=None, past_v=None):
     if past_k is not None:
         k = np.concatenate([past_k, k], axis=0)
         v = np.concatenate([past_v, v], axis=0)
-    keys = np.arange(k.shape[0])
-    dist = pos[:, None] - keys[None, :]                                   # i - j
     window = m["mask"]["size"] if m.get("mask") else None
-    seen = (dist >= 0) & ((dist < window) if window else True)
-    slopes = head_slopes(H)
-    out = np.zeros((T, H, e))
-    for hd in range(H):
-        kv = hd // (H // G)
-        s = (q[:, hd] @ k[:, kv].T) * m["scale"] - slopes[hd] * dist
-        s = np.where(seen, s, -np.inf)
-        s = s - s.max(axis=1, keepdims=True)
-        p = np.exp(s)
-        p /= p.sum(axis=1, keepdims=True)
-        out[:, hd] = p @ v[:, kv]
+    out = biased_attention(q, k, v, pos, m["scale"], window, head_slopes(H))
     return out.reshape(T, H * e) @ w[f"{name}.o"].T, k, v
 
 
