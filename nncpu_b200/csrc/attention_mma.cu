@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(128, 3)
 prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
                const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
                const int* __restrict__ cu_seqlens, const int* __restrict__ tok_pos, __nv_bfloat16* __restrict__ out,
-               int n_seqs, int n_heads, int n_kv, float scale2, int window) {
+               int n_seqs, int n_heads, int n_kv, float scale2, int window, float slope_base) {
     constexpr int kTileBytes = kPage * HD * 2;           // one page of K or of V for one head
     constexpr int kChunks = HD / 8;                      // 16-byte chunks per row
     extern __shared__ __align__(128) uint8_t fa_smem[];  // [2 stages][K tile | V tile]
@@ -155,6 +155,9 @@ prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     const int page_lo = key_lo / kPage, page_hi = key_hi / kPage;
     const int* table = block_table + (size_t)seq * bt_stride;
     const int kvh = h / (n_heads / n_kv);
+    // a distance bias: this head takes slope * (query position - key position) off its scaled scores (0: none);
+    // the softmax works in powers of two, so the slope carries log2(e) like the scale
+    const float slope2 = slope_base != 0.0f ? exp2f(-slope_base * (float)(h + 1) / (float)n_heads) * kLog2e : 0.0f;
 
     // this warp's rows: q0 + 16 * warp + r and + 8
     const int row_lo = 16 * warp + r, row_hi = row_lo + 8;
@@ -238,9 +241,10 @@ prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
                 for (int e = 0; e < 4; ++e) {
                     const int row = e >> 1;
                     float v = s[t][e] * scale2;
-                    if (!full) {
+                    if (!full || slope2 != 0.0f) {
                         const int key = k_base + t * 8 + 2 * c + (e & 1);
-                        if (key < lim_lo[row] || key > lim_hi[row]) v = -INFINITY;
+                        v -= slope2 * (float)(lim_hi[row] - key);
+                        if (!full && (key < lim_lo[row] || key > lim_hi[row])) v = -INFINITY;
                     }
                     s[t][e] = v;
                     mx[row] = fmaxf(mx[row], v);
@@ -333,6 +337,7 @@ struct FusedQK {
     const float2* cs;         // [n_tok, HD / 2] (cos, sin) of the tokens' positions, or null: no rotation
     __nv_bfloat16* k_pages;   // the cache, writable; null: the keys and values are another entry's, nothing is appended
     __nv_bfloat16* v_pages;
+    float slope_base;         // not of the projections: b != 0 gives head h the distance bias 2^(-b (h + 1) / n_heads) * (pos - key)
 };
 
 // One head's HD float32 values through norm (if gamma) and rotation (if cs) to bfloat16; a warp's job.  A lane holds
@@ -513,10 +518,20 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
 #pragma unroll
         for (int tt = 0; tt < NT; ++tt) {
             float* sv = s[tt];
-            sv[0] = lo_ok ? sv[0] * scale2 : -INFINITY;
-            sv[1] = lo_ok ? sv[1] * scale2 : -INFINITY;
-            sv[2] = hi_ok ? sv[2] * scale2 : -INFINITY;
-            sv[3] = hi_ok ? sv[3] * scale2 : -INFINITY;
+            float b_lo[2] = {0.0f, 0.0f}, b_hi[2] = {0.0f, 0.0f};
+            if (f.slope_base != 0.0f) {      // the distance bias of the two heads this lane holds (columns 2c, 2c + 1)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int head = kvh * G + tt * 8 + 2 * c + j;
+                    const float slope2 = exp2f(-f.slope_base * (float)(head + 1) / (float)n_heads) * kLog2e;
+                    b_lo[j] = slope2 * (float)(pos - (k0 + r));
+                    b_hi[j] = slope2 * (float)(pos - (k0 + r + 8));
+                }
+            }
+            sv[0] = lo_ok ? sv[0] * scale2 - b_lo[0] : -INFINITY;
+            sv[1] = lo_ok ? sv[1] * scale2 - b_lo[1] : -INFINITY;
+            sv[2] = hi_ok ? sv[2] * scale2 - b_hi[0] : -INFINITY;
+            sv[3] = hi_ok ? sv[3] * scale2 - b_hi[1] : -INFINITY;
             float mx0 = fmaxf(sv[0], sv[2]), mx1 = fmaxf(sv[1], sv[3]);
 #pragma unroll
             for (int sh = 4; sh <= 16; sh <<= 1) {
@@ -653,7 +668,8 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
 template <int HD>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int bt_stride,
                   const int* tok_seq, const int* tok_pos, void* out, float* scratch, int n_tok, int n_heads, int n_kv,
-                  float scale, int window, int n_splits, cudaStream_t stream, const FusedQK* fused = nullptr) {
+                  float scale, int window, int n_splits, cudaStream_t stream, const FusedQK* fused = nullptr,
+                  float slope_base = 0.0f) {
     using Kernel = void (*)(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*, const int*, int, const int*,
                             const int*, __nv_bfloat16*, float*, float*, int, int, float, int, const FusedQK);
     const int G = n_heads / n_kv;
@@ -666,7 +682,8 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
     const Kernel from_qkv = cluster ? (G <= 8 ? (Kernel)decode_kernel<HD, 1, true, true> : (Kernel)decode_kernel<HD, 2, true, true>)
                                     : (G <= 8 ? (Kernel)decode_kernel<HD, 1, false, true> : (Kernel)decode_kernel<HD, 2, false, true>);
     const Kernel kernel = fused ? from_qkv : plain;
-    const FusedQK f = fused ? *fused : FusedQK{};
+    FusedQK f = fused ? *fused : FusedQK{};
+    f.slope_base = slope_base;
     const size_t stages = (size_t)kDecodeStages * 2 * kPage * HD * 2;
     const size_t merge = (size_t)5 * G * (HD + 2) * sizeof(float);
     const size_t smem = stages > merge ? stages : merge;
@@ -704,7 +721,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
 template <int HD>
 int launch_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int bt_stride,
                    const int* cu_seqlens, const int* tok_pos, void* out, int n_tok, int n_seqs, int n_heads, int n_kv,
-                   float scale, int window, cudaStream_t stream) {
+                   float scale, int window, float slope_base, cudaStream_t stream) {
     const int max_tiles = n_tok / 64 + n_seqs;
     constexpr int smem = 2 * 2 * kPage * HD * 2;
     static bool configured[64] = {};
@@ -716,7 +733,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
     prefill_kernel<HD><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
                                                  (const __nv_bfloat16*)v_pages, block_table, bt_stride, cu_seqlens,
                                                  tok_pos, (__nv_bfloat16*)out, n_seqs, n_heads, n_kv, scale * kLog2e,
-                                                 window);
+                                                 window, slope_base);
     NN_LAUNCH_OK("attention prefill");
     return 0;
 }
@@ -741,7 +758,7 @@ extern "C" int nncpu_attention_decode_mma(const void* q, const void* k_pages, co
                                           const int* block_table, int bt_stride, const int* tok_seq,
                                           const int* tok_pos, void* out, float* scratch, long scratch_floats,
                                           int n_tok, int n_heads, int n_kv, int hd, float scale, int window,
-                                          int n_splits, void* stream) {
+                                          int n_splits, float slope_base, void* stream) {
     NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
              "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
              "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
@@ -756,9 +773,9 @@ extern "C" int nncpu_attention_decode_mma(const void* q, const void* k_pages, co
     if (n_tok == 0) return 0;
     if (hd == 64)
         return launch_decode<64>(q, k_pages, v_pages, block_table, bt_stride, tok_seq, tok_pos, out, scratch, n_tok,
-                                 n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream);
+                                 n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream, nullptr, slope_base);
     return launch_decode<128>(q, k_pages, v_pages, block_table, bt_stride, tok_seq, tok_pos, out, scratch, n_tok,
-                              n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream);
+                              n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream, nullptr, slope_base);
 }
 
 // The same from the float32 projections: qkv [n_tok, per_tok * hd] holds, per token, the heads of q and, if `append`,
@@ -807,7 +824,7 @@ extern "C" int nncpu_attention_decode_mma_from_qkv(const float* qkv, const void*
 extern "C" int nncpu_attention_prefill_mma(const void* q, const void* k_pages, const void* v_pages,
                                            const int* block_table, int bt_stride, const int* cu_seqlens,
                                            const int* tok_pos, void* out, int n_tok, int n_seqs, int n_heads,
-                                           int n_kv, int hd, float scale, int window, void* stream) {
+                                           int n_kv, int hd, float scale, int window, float slope_base, void* stream) {
     NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
              "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
              "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
@@ -815,9 +832,9 @@ extern "C" int nncpu_attention_prefill_mma(const void* q, const void* k_pages, c
     if (n_tok == 0 || n_seqs == 0) return 0;
     if (hd == 64)
         return launch_prefill<64>(q, k_pages, v_pages, block_table, bt_stride, cu_seqlens, tok_pos, out, n_tok, n_seqs,
-                                  n_heads, n_kv, scale, window, (cudaStream_t)stream);
+                                  n_heads, n_kv, scale, window, slope_base, (cudaStream_t)stream);
     return launch_prefill<128>(q, k_pages, v_pages, block_table, bt_stride, cu_seqlens, tok_pos, out, n_tok, n_seqs,
-                               n_heads, n_kv, scale, window, (cudaStream_t)stream);
+                               n_heads, n_kv, scale, window, slope_base, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -897,5 +914,5 @@ extern "C" int nncpu_attention_decode_mma_static(const void* q, const void* k_pa
     float* scratch = nullptr;
     if (int e = static_scratch(&scratch)) return e;
     return nncpu_attention_decode_mma(q, k_pages, v_pages, block_table, bt_stride, tok_seq, tok_pos, out, scratch,
-                                      kStaticScratchFloats, n_tok, n_heads, n_kv, hd, scale, window, n_splits, stream);
+                                      kStaticScratchFloats, n_tok, n_heads, n_kv, hd, scale, window, n_splits, 0.0f, stream);
 }

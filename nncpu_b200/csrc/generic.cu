@@ -357,7 +357,7 @@ qk_norm_rope_append_fast_kernel(const float* __restrict__ qkv, const void* __res
                                 const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                                 const int* __restrict__ block_table, int bt_stride, __nv_bfloat16* __restrict__ k_pages,
                                 __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ q_out, int n_tok,
-                                int n_heads, int n_kv) {
+                                int n_heads, int n_kv, float temp_coef, int temp_every) {
     constexpr int hd = 32 * EPL, half = hd / 2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per_tok = n_heads + 2 * n_kv;
@@ -395,6 +395,11 @@ qk_norm_rope_append_fast_kernel(const float* __restrict__ qkv, const void* __res
     }
     __nv_bfloat16* dst;
     if (is_q) {
+        if (temp_coef != 0.0f) {       // the query temperature of the token's position
+            const float temp = 1.0f + temp_coef * logf((float)((tok_pos[t] + 1) / temp_every) + 1.0f);
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) x[e] *= temp;
+        }
         dst = q_out + ((size_t)t * n_heads + h) * hd;
     } else {
         const int seq = tok_seq[t];
@@ -427,17 +432,19 @@ extern "C" int nncpu_qk_norm_rope_append(const void* qkv, int in_dt, const void*
     NN_CHECK(hd <= 1024, "qk_norm_rope_append: head size %d is above 1024", hd);
     if (n_tok == 0) return 0;
     if (in_dt == DT_F32 && q_dt == DT_BF16 && (n_kv == 0 || kv_dt == DT_BF16) && (hd == 64 || hd == 128) && vd == hd &&
-        temp_coef == 0.0f && (cs == nullptr || 2 * rot_half == hd) && (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0) {
+        (cs == nullptr || 2 * rot_half == hd) && (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0) {
         const long n_items = (long)n_tok * (n_heads + 2 * n_kv);
         const unsigned n_blocks = (unsigned)((n_items + 7) / 8);
         if (hd == 128)
             qk_norm_rope_append_fast_kernel<4><<<n_blocks, 256, 0, (cudaStream_t)stream>>>(
                 (const float*)qkv, q_gamma, k_gamma, g_dt, eps, (const float2*)cs, tok_seq, tok_pos, block_table,
-                bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, (__nv_bfloat16*)q_out, n_tok, n_heads, n_kv);
+                bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, (__nv_bfloat16*)q_out, n_tok, n_heads, n_kv,
+                temp_coef, temp_every);
         else
             qk_norm_rope_append_fast_kernel<2><<<n_blocks, 256, 0, (cudaStream_t)stream>>>(
                 (const float*)qkv, q_gamma, k_gamma, g_dt, eps, (const float2*)cs, tok_seq, tok_pos, block_table,
-                bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, (__nv_bfloat16*)q_out, n_tok, n_heads, n_kv);
+                bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, (__nv_bfloat16*)q_out, n_tok, n_heads, n_kv,
+                temp_coef, temp_every);
         NN_LAUNCH_OK("qk_norm_rope_append");
         return 0;
     }

@@ -389,7 +389,7 @@ def attention_decode_scratch_floats(n_tok: int, n_heads: int, n_kv: int, head_di
 
 
 def attention_decode_mma(q, k_pages, v_pages, block_table, tok_seq, tok_pos, out, scratch, n_heads: int, n_kv: int,
-                         head_dim: int, scale: float, window: int, n_splits: int) -> None:
+                         head_dim: int, scale: float, window: int, n_splits: int, slope_base: float = 0.0) -> None:
     """One token per sequence; each token's keys are cut into ``n_splits``
     splits that run in parallel.  With ``scratch`` (float32,
     ``attention_decode_scratch_floats`` elements) a second kernel merges them;
@@ -401,7 +401,7 @@ def attention_decode_mma(q, k_pages, v_pages, block_table, tok_seq, tok_pos, out
     _call("attention_mma", "nncpu_attention_decode_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
           _i(block_table.shape[1]), _ptr(tok_seq), _ptr(tok_pos), _ptr(out), _ptr(scratch),
           ctypes.c_long(0 if scratch is None else scratch.numel()), _i(n), _i(n_heads), _i(n_kv), _i(head_dim),
-          _f(scale), _i(window), _i(n_splits), _stream())
+          _f(scale), _i(window), _i(n_splits), _f(slope_base), _stream())
 
 
 def attention_decode_mma_from_qkv(qkv, q_gamma, k_gamma, eps, cos_sin, k_pages, v_pages, append: bool, block_table,
@@ -427,13 +427,13 @@ def attention_decode_mma_from_qkv(qkv, q_gamma, k_gamma, eps, cos_sin, k_pages, 
 
 
 def attention_prefill_mma(q, k_pages, v_pages, block_table, cu_seqlens, tok_pos, out, n_seqs: int, n_heads: int,
-                          n_kv: int, head_dim: int, scale: float, window: int) -> None:
-    """Any number of new tokens per sequence, at consecutive positions."""
+                          n_kv: int, head_dim: int, scale: float, window: int, slope_base: float = 0.0) -> None:
+    """Any number of new tokens per sequence, at consecutive positions.  ``slope_base`` as in ``attention``."""
     n = q.shape[0]
     assert q.shape == (n, n_heads * head_dim) and out.shape == q.shape and cu_seqlens.numel() >= n_seqs + 1
     _call("attention_mma", "nncpu_attention_prefill_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
           _i(block_table.shape[1]), _ptr(cu_seqlens), _ptr(tok_pos), _ptr(out), _i(n), _i(n_seqs), _i(n_heads),
-          _i(n_kv), _i(head_dim), _f(scale), _i(window), _stream())
+          _i(n_kv), _i(head_dim), _f(scale), _i(window), _f(slope_base), _stream())
 
 
 def attention_prefill_tc_supported(n_heads: int, n_kv: int, head_dim: int, *tensors) -> bool:

@@ -44,8 +44,11 @@ class Attention(Mixer):
         self.kv_size = 0 if reads_other_cache else s.n_kv_heads * s.head_dim
         self.v_size = 0 if reads_other_cache else s.n_kv_heads * self.v_dim
         self.out_size = s.n_heads * self.v_dim
-        # what the tensor-core attention kernels and the fused epilogues do not know: they are left to the 32-bit kernel
-        self.plain_core = self.v_dim != s.head_dim or s.slope_base != 0.0 or s.q_temp_coef != 0.0
+        # Value heads of their own size are known to the 32-bit kernel alone.  A distance bias or a query temperature
+        # keeps the step off the fused epilogues and off the tcgen05 prompt kernel (which know neither): the
+        # temperature is applied where q is made, the bias inside the mma.sync kernels for prompts and decode steps.
+        self.plain_core = self.v_dim != s.head_dim
+        self.unfused = self.plain_core or s.slope_base != 0.0 or s.q_temp_coef != 0.0
         self.q_temp = (s.q_temp_coef, s.q_temp_every) if s.q_temp_coef != 0.0 else None
         self.position = None if s.position is None else base.build("position", s.position)
 
@@ -163,7 +166,7 @@ class Attention(Mixer):
         """Whether this step's attention can start from the float32 projections: a decode step on the tensor-core
         kernel, every lane of a head rotated (or none), norm weights of one type."""
         s = self.spec
-        return (not self.plain_core and ctx.is_decode and self.rt.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
+        return (not self.unfused and ctx.is_decode and self.rt.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
                 and ops.attention_mma_supported(s.n_heads, s.n_kv_heads, s.head_dim)
                 and (self.position is None or self.position.half * 2 == s.head_dim)
                 and (self.q_gamma is None or self.k_gamma is None or self.q_gamma.dtype == self.k_gamma.dtype))
@@ -182,7 +185,7 @@ class Attention(Mixer):
         s = self.spec
         if isinstance(x, base.DeferredNorm):
             x = x.x_gamma
-        return (not self.plain_core and not self.shared_kv and self.b_qkv is None and x.dtype == torch.bfloat16
+        return (not self.unfused and not self.shared_kv and self.b_qkv is None and x.dtype == torch.bfloat16
                 and self.w_qkv.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
                 and (self.position is None or (self.position.tables_by_pair and self.position.half * 2 == s.head_dim))
                 and ops.linear_tc_qkv_supported(x, s.n_heads, s.n_kv_heads, s.head_dim))
@@ -198,8 +201,9 @@ class Attention(Mixer):
         elif ctx.is_decode:
             n_splits, scratch = self._decode_splits(ctx)
             ops.attention_decode_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos,
-                                     attn, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, n_splits)
-        elif ctx.n_tokens >= 32 * ctx.n_seqs and ops.attention_prefill_tc_supported(
+                                     attn, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, n_splits,
+                                     s.slope_base)
+        elif not self.unfused and ctx.n_tokens >= 32 * ctx.n_seqs and ops.attention_prefill_tc_supported(
                 s.n_heads, s.n_kv_heads, s.head_dim, q, cache.k_pages, attn):
             # prompts: 128-row tiles on the tcgen05 tensor cores
             ops.attention_prefill_tc(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.cu_seqlens, ctx.tok_pos,
@@ -208,4 +212,5 @@ class Attention(Mixer):
         else:
             # a few new tokens per sequence: 64-row tiles
             ops.attention_prefill_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.cu_seqlens, ctx.tok_pos,
-                                      attn, ctx.n_seqs, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window)
+                                      attn, ctx.n_seqs, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window,
+                                      s.slope_base)

@@ -251,6 +251,38 @@ def test_biased_attention_alone(dtype, nh, nkv, hd, vd, window):
     check(out, want, 2e-5 if dtype == "float32" else 2e-2, "attention with distance bias")
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 64, 100), (2, 1, 128, 64), (8, 1, 64, 40), (16, 1, 64, 0), (12, 4, 128, 200)])
+def test_biased_attention_on_the_tensor_core_kernels(nh, nkv, hd, window):
+    """The bfloat16 kernels for prompts and for decode steps with the distance bias: three sequences (a portion of
+    9 tokens, a whole prompt of 67, a portion of 130 that crosses two pages), then one token each, with the keys in
+    one split and in two."""
+    lens, new = [150, 67, 300], [9, 67, 130]
+    g = torch.Generator().manual_seed(nh + hd)
+    kp, vp, table, ks, vs = scatter_pages(12, nkv, hd, lens, torch.bfloat16, seed=3)
+    slopes = P.head_slopes(nh)
+    q = [torch.randn(n, nh, hd, generator=g).bfloat16() for n in new]
+    n = sum(new)
+    cu = torch.tensor(np.cumsum([0] + new), dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([p for b in range(3) for p in range(lens[b] - new[b], lens[b])], dtype=torch.int32, device=DEV)
+    out = torch.empty(n, nh * hd, dtype=torch.bfloat16, device=DEV)
+    ops.attention_prefill_mma(torch.cat(q).view(n, -1).to(DEV), kp, vp, table, cu, tok_pos, out, 3, nh, nkv, hd, 0.2, window, 8.0)
+    want = torch.cat([torch.from_numpy(P.biased_attention(
+        q[b].double().numpy(), ks[b].double().numpy(), vs[b].double().numpy(), range(lens[b] - new[b], lens[b]), 0.2,
+        window or None, slopes)) for b in range(3)]).view(n, -1)
+    check(out, want, 2e-2, "prompt kernel with distance bias")
+    last = torch.stack([q[b][-1] for b in range(3)]).view(3, -1).to(DEV)
+    seq = torch.arange(3, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)
+    want = torch.stack([want[int(cu[b + 1]) - 1] for b in range(3)])
+    for n_splits in (1, 2):
+        scratch = None
+        if n_splits > 1:
+            scratch = torch.empty(ops.attention_decode_scratch_floats(3, nh, nkv, hd, n_splits), device=DEV)
+        got = torch.empty(3, nh * hd, dtype=torch.bfloat16, device=DEV)
+        ops.attention_decode_mma(last, kp, vp, table, seq, pos, got, scratch, nh, nkv, hd, 0.2, window, n_splits, 8.0)
+        check(got, want, 2e-2, f"decode kernel with distance bias, {n_splits} splits")
+
+
 @pytest.mark.parametrize("window", [1, 5, 64, 65, 100])
 def test_window_edge_one_key_inside_one_outside(window):
     """One key's score stands out (its query and key are scaled up).  At distance window - 1 it is seen and the
