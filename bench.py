@@ -228,7 +228,118 @@ WORKLOADS = {
     "14b-unequal": dict(model="14b", batch=16, prompt=(128, 2048), decode=256),
     "32b": dict(model="32b", batch=8, prompt=(2048, 2048), decode=512),
     "long-context": dict(model="8b"),
+    "romepel": dict(model="8b"),
 }
+
+# `--workload romepel`: the Romepel design (recurrent gla layers, windowed attention with a distance bias, sandwich
+# norms, a dense xIELU feed-forward) at sizes that resemble a real model's layers, beside Qwen3 layers of equal width,
+# depth, head counts, window and parameter count (a dense feed-forward of 1.5 x the gated one's width has its weights).
+ROMEPEL_SIZES = {
+    "2048": dict(width=2048, layers=8, heads=16, kv_heads=4, dim=128, inter=6144, window=512, gla_heads=8, gla_dim=128,
+                 gla_vdim=256, rank=32, vocab=32768),
+    "4096": dict(width=4096, layers=8, heads=32, kv_heads=8, dim=128, inter=12288, window=1024, gla_heads=16, gla_dim=128,
+                 gla_vdim=256, rank=64, vocab=65536),
+}
+
+
+def romepel_configs(z: dict):
+    """(Romepel configuration, the closest existing model's: Qwen3 with every layer on the same sliding window)."""
+    from nncpu_b200.config import config_from_dict
+    att = {"type": "attention", "mlp": {"kind": "dense", "ff": z["inter"] * 3 // 2},
+           "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                     "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}, "q_temp": {"coef": 0.3, "every": 128}}}
+    gla = {"type": "gla", "mlp": {"kind": "dense", "ff": z["inter"] * 3 // 2},
+           "mixer": {"heads": z["gla_heads"], "dim": z["gla_dim"], "vdim": z["gla_vdim"], "tau": 16.0, "rank": z["rank"]}}
+    layers = [gla if i % 3 == 0 else att for i in range(z["layers"])]
+    rom = config_from_dict({"architecture": "Romepel", "vocab": z["vocab"], "width": z["width"], "max_positions": CONTEXT,
+                            "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": layers})
+    qwen = config_from_dict(dict(QWEN3_8B, num_hidden_layers=z["layers"], hidden_size=z["width"],
+                                 num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
+                                 intermediate_size=z["inter"], vocab_size=z["vocab"], use_sliding_window=True,
+                                 sliding_window=z["window"], max_window_layers=0))
+    return rom, qwen
+
+
+def phase_table(totals: dict, calls: int, pk: dict) -> dict:
+    """Per phase of the profiler: milliseconds per step and, where the phase states its bytes and operations, the
+    fraction of the roofline (the slower of bytes / copy bandwidth and operations / tensor throughput, over the time)."""
+    out = {}
+    for name, t in totals.items():
+        ms = t["ms"] / calls
+        row = {"ms": round(ms, 4)}
+        ideal = max(t["bytes"] / calls / (pk["hbm_gbs"] * 1e9), t["flops"] / calls / (pk["bf16_tflops"] * 1e12))
+        if ideal > 0 and ms > 0:
+            row["roofline_frac"] = round(ideal / (ms / 1e3), 4)
+        out[name] = row
+    return out
+
+
+def run_design_point(cfg, vocab: int, pk: dict, batch: int = 8, decode_steps: int = 128) -> dict:
+    """One model: a 2 048-token prompt (best of 3 after a warm-up), then `decode_steps` device-timed greedy decode
+    steps of `batch` sequences after 8 warm-up steps, then both kinds of step kernel by kernel under the phase profiler."""
+    import torch
+    from nncpu_b200 import Engine, Model, perf_enable, perf_reset, perf_totals
+    from nncpu_b200.kernels import ops
+    model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    g = torch.Generator().manual_seed(13)
+    out = {"weight_bytes_per_step": model.weight_bytes_per_step()}
+    engine = Engine(model, max_tokens=(PROMPT + 256) * batch, max_seq_len=PROMPT + 256, max_step_tokens=PROMPT)
+    prompt = torch.randint(0, vocab, (PROMPT,), generator=g).tolist()
+    best = None
+    for r in range(4):
+        slot = engine.alloc_slot()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        engine.step([slot], [prompt])
+        b.record()
+        torch.cuda.synchronize()
+        engine.free_slot(slot)
+        if r > 0:
+            best = a.elapsed_time(b) if best is None else min(best, a.elapsed_time(b))
+    out["prefill"] = {"tokens": PROMPT, "ms": round(best, 3), "tokens_per_s": round(PROMPT / (best / 1e3), 1)}
+    slots = [engine.alloc_slot() for _ in range(batch)]
+    firsts = []
+    for s in slots:
+        logits = engine.step([s], [torch.randint(0, vocab, (PROMPT,), generator=g).tolist()])
+        ids = torch.empty(1, dtype=torch.int32, device=logits.device)
+        ops.argmax(logits, ids)
+        firsts += ids.tolist()
+    ms, _, _ = timed_decode(engine, slots, firsts, decode_steps, 8)
+    out["decode"] = {"batch": batch, "steps": decode_steps, "ms_per_step": round(ms / decode_steps, 4),
+                     "tokens_per_s": round(batch * decode_steps / (ms / 1e3), 1),
+                     "weights_hbm_frac": round(out["weight_bytes_per_step"] / (ms / decode_steps / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+    perf_enable(True)
+    engine.step(slots, [[1]] * batch)
+    perf_reset()
+    for _ in range(4):
+        engine.step(slots, [[1]] * batch)
+    out["decode_phases"] = phase_table(perf_totals(), 4, pk)
+    for s in slots:
+        engine.free_slot(s)
+    slot = engine.alloc_slot()
+    engine.step([slot], [prompt])           # once kernel by kernel with the profiler on, not timed
+    engine.free_slot(slot)
+    slot = engine.alloc_slot()
+    perf_reset()
+    engine.step([slot], [prompt])
+    out["prefill_phases"] = phase_table(perf_totals(), 1, pk)
+    perf_enable(False)
+    perf_reset()
+    model.rt.check_status()
+    del engine, model
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_romepel() -> dict:
+    pk = peaks()
+    out = {"workload": "romepel", "dtype": "bf16", "peaks": pk["source"], "prompt": PROMPT,
+           "data": "synthetic: random weights, uniform random token ids", "sizes": {}}
+    for name, z in ROMEPEL_SIZES.items():
+        rom, qwen = romepel_configs(z)
+        out["sizes"][name] = {"config": z, "romepel": run_design_point(rom, z["vocab"], pk),
+                              "qwen3_same_size": run_design_point(qwen, z["vocab"], pk)}
+    return out
 
 
 def run_long_context() -> dict:
@@ -395,7 +506,8 @@ def main() -> int:
         print(json.dumps(fp32_check(cfg, args.model)))
         return 0
     if args.workload:
-        print(json.dumps(run_long_context() if args.workload == "long-context" else run_workload(args.workload)))
+        special = {"long-context": run_long_context, "romepel": run_romepel}
+        print(json.dumps(special[args.workload]() if args.workload in special else run_workload(args.workload)))
         return 0
     model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
 

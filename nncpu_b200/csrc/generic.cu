@@ -93,7 +93,7 @@ __global__ void rmsnorm_kernel(const void* __restrict__ x, int x_dt, const void*
 template <int kVec>
 __global__ void __launch_bounds__(256)
 rmsnorm_f32_kernel(const float* __restrict__ x, const void* __restrict__ gamma, int g_dt, void* __restrict__ y,
-                   int y_dt, const int* __restrict__ rows, int dim, float eps) {
+                   int y_dt, const int* __restrict__ rows, int dim, float eps, float gamma_offset, int accumulate) {
     __shared__ float scratch[33];
     // launched to start while the kernel before it ends: the product that follows may set itself up meanwhile
     let_next_kernel_start();
@@ -125,9 +125,14 @@ rmsnorm_f32_kernel(const float* __restrict__ x, const void* __restrict__ gamma, 
         float o[4] = {v[j].x * scale, v[j].y * scale, v[j].z * scale, v[j].w * scale};
         if (gamma) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) o[e] *= ld_f(gamma, 4 * i + e, g_dt);
+            for (int e = 0; e < 4; ++e) o[e] *= ld_f(gamma, 4 * i + e, g_dt) + gamma_offset;
         }
         const size_t at = (size_t)r_out * dim + 4 * i;
+        if (accumulate) {          // float32 y (checked by the launcher): the norm is added to what y holds
+            if (r_in < 0) continue;
+            const float4 was = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(y) + at);
+            o[0] += was.x; o[1] += was.y; o[2] += was.z; o[3] += was.w;
+        }
         if (y_dt == DT_BF16) {
             __nv_bfloat162 h[2] = {__floats2bfloat162_rn(o[0], o[1]), __floats2bfloat162_rn(o[2], o[3])};
             *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(y) + at) = *reinterpret_cast<uint2*>(h);
@@ -143,7 +148,7 @@ extern "C" int nncpu_rmsnorm(const void* x, int x_dt, const void* gamma, int g_d
     NN_CHECK(n_rows >= 0 && dim > 0, "rmsnorm: %d rows of %d", n_rows, dim);
     NN_CHECK(!accumulate || x != y, "rmsnorm: a norm cannot be added to its own input");
     if (n_rows == 0) return 0;
-    if (gamma_offset == 0.0f && !accumulate && x_dt == DT_F32 && dim % 4 == 0 && dim >= 1024 && dim <= 256 * 4 * 8 && (uintptr_t)x % 16 == 0 &&
+    if ((!accumulate || y_dt == DT_F32) && x_dt == DT_F32 && dim % 4 == 0 && dim >= 1024 && dim <= 256 * 4 * 8 && (uintptr_t)x % 16 == 0 &&
         (uintptr_t)y % 16 == 0) {
         const float* xf = (const float*)x;
         cudaLaunchConfig_t cfg = {};
@@ -154,7 +159,8 @@ extern "C" int nncpu_rmsnorm(const void* x, int x_dt, const void* gamma, int g_d
         cfg.attrs = attr;
         cfg.numAttrs = overlap_attribute(attr);
         const auto kernel = dim <= 256 * 4 * 2 ? rmsnorm_f32_kernel<2> : dim <= 256 * 4 * 4 ? rmsnorm_f32_kernel<4> : rmsnorm_f32_kernel<8>;
-        const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, xf, gamma, g_dt, y, y_dt, rows, dim, eps);
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, xf, gamma, g_dt, y, y_dt, rows, dim, eps, gamma_offset,
+                                                 accumulate);
         NN_CHECK(e == cudaSuccess, "rmsnorm: launch failed: %s", cudaGetErrorString(e));
         return 0;
     }
@@ -162,6 +168,82 @@ extern "C" int nncpu_rmsnorm(const void* x, int x_dt, const void* gamma, int g_d
     rmsnorm_kernel<<<n_rows, threads, 0, (cudaStream_t)stream>>>(x, x_dt, gamma, g_dt, y, y_dt, rows, dim, eps,
                                                                  gamma_offset, accumulate);
     NN_LAUNCH_OK("rmsnorm");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// The two norms that meet between two sublayers of a "sandwich" layer, in one pass:
+//     r <- r + norm(b) * (g1 + off1)      (the norm that closes a sublayer, added to the residual stream r)
+//     y  = norm(r) * (g2 + off2)          (the norm that opens the next sublayer)
+// b and r are float32 rows of `dim`; a thread keeps its part of the row in registers between the two sums, so
+// b and r are read once and r and y written once.  dim <= 256 * 4 * kVec, a multiple of 4.
+// ---------------------------------------------------------------------------
+template <int kVec>
+__global__ void __launch_bounds__(256)
+rmsnorm_pair_kernel(const float* __restrict__ b, float* __restrict__ r, const void* __restrict__ g1, float off1,
+                    const void* __restrict__ g2, float off2, int g_dt, void* __restrict__ y, int y_dt, int dim,
+                    float eps1, float eps2) {
+    __shared__ float scratch[33];
+    const int row = blockIdx.x, n4 = dim >> 2;
+    float4 v[kVec];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+        const int i = threadIdx.x + j * 256;
+        v[j] = i < n4 ? reinterpret_cast<const float4*>(b + (size_t)row * dim)[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+        ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float s1 = 1.0f / sqrtf(ss * (1.0f / (float)dim) + eps1);
+    float ss2 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i >= n4) continue;
+        float4* at = reinterpret_cast<float4*>(r + (size_t)row * dim) + i;
+        const float4 was = *at;
+        float o[4] = {v[j].x * s1, v[j].y * s1, v[j].z * s1, v[j].w * s1};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[e] *= ld_f(g1, 4 * i + e, g_dt) + off1;
+        v[j] = make_float4(was.x + o[0], was.y + o[1], was.z + o[2], was.w + o[3]);
+        *at = v[j];
+        ss2 = fmaf(v[j].x, v[j].x, ss2); ss2 = fmaf(v[j].y, v[j].y, ss2);
+        ss2 = fmaf(v[j].z, v[j].z, ss2); ss2 = fmaf(v[j].w, v[j].w, ss2);
+    }
+    ss2 = block_sum(ss2, scratch);
+    const float s2 = 1.0f / sqrtf(ss2 * (1.0f / (float)dim) + eps2);
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i >= n4) continue;
+        float o[4] = {v[j].x * s2, v[j].y * s2, v[j].z * s2, v[j].w * s2};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[e] *= ld_f(g2, 4 * i + e, g_dt) + off2;
+        const size_t at = (size_t)row * dim + 4 * i;
+        if (y_dt == DT_BF16) {
+            __nv_bfloat162 h[2] = {__floats2bfloat162_rn(o[0], o[1]), __floats2bfloat162_rn(o[2], o[3])};
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(y) + at) = *reinterpret_cast<uint2*>(h);
+        } else {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(y) + at) = make_float4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
+extern "C" int nncpu_rmsnorm_pair_supported(int dim) { return dim > 0 && dim % 4 == 0 && dim <= 256 * 4 * 8; }
+
+extern "C" int nncpu_rmsnorm_pair(const float* b, float* r, const void* g1, float off1, float eps1, const void* g2,
+                                  float off2, float eps2, int g_dt, void* y, int y_dt, int n_rows, int dim, void* stream) {
+    NN_CHECK(n_rows >= 0 && nncpu_rmsnorm_pair_supported(dim), "rmsnorm_pair: %d rows of %d", n_rows, dim);
+    NN_CHECK((uintptr_t)b % 16 == 0 && (uintptr_t)r % 16 == 0 && (uintptr_t)y % 16 == 0 && b != r,
+             "rmsnorm_pair: rows must be 16-byte aligned and the branch must not be the stream");
+    if (n_rows == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dim <= 256 * 4) rmsnorm_pair_kernel<1><<<n_rows, 256, 0, st>>>(b, r, g1, off1, g2, off2, g_dt, y, y_dt, dim, eps1, eps2);
+    else if (dim <= 256 * 4 * 2) rmsnorm_pair_kernel<2><<<n_rows, 256, 0, st>>>(b, r, g1, off1, g2, off2, g_dt, y, y_dt, dim, eps1, eps2);
+    else if (dim <= 256 * 4 * 4) rmsnorm_pair_kernel<4><<<n_rows, 256, 0, st>>>(b, r, g1, off1, g2, off2, g_dt, y, y_dt, dim, eps1, eps2);
+    else rmsnorm_pair_kernel<8><<<n_rows, 256, 0, st>>>(b, r, g1, off1, g2, off2, g_dt, y, y_dt, dim, eps1, eps2);
+    NN_LAUNCH_OK("rmsnorm_pair");
     return 0;
 }
 
@@ -603,10 +685,34 @@ __global__ void xielu_kernel(const void* __restrict__ x, int in_dt, const void* 
     st_f(out, (size_t)idx, out_dt, y);
 }
 
+// The prompt's case: float32 in, bfloat16 out, four elements a thread (16 bytes in, 8 out).
+__global__ void __launch_bounds__(256)
+xielu_f32_bf16_kernel(const float4* __restrict__ x, const void* __restrict__ params, int p_dt,
+                      uint2* __restrict__ out, long n4) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n4) return;
+    const float a_pos = softplus_f(ld_f(params, 0, p_dt));
+    const float a_neg = 0.5f + softplus_f(ld_f(params, 1, p_dt));
+    const float4 v = x[idx];
+    const float z[4] = {v.x, v.y, v.z, v.w};
+    float y[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+        y[e] = z[e] > 0.0f ? fmaf(a_pos * z[e], z[e], 0.5f * z[e]) : fmaf(a_neg, expm1f(z[e]) - z[e], 0.5f * z[e]);
+    __nv_bfloat162 h[2] = {__floats2bfloat162_rn(y[0], y[1]), __floats2bfloat162_rn(y[2], y[3])};
+    out[idx] = *reinterpret_cast<uint2*>(h);
+}
+
 extern "C" int nncpu_xielu(const void* x, int in_dt, const void* params, int p_dt, void* out, int out_dt, long n,
                            void* stream) {
     NN_CHECK(n >= 0 && params != nullptr, "xielu: %ld elements", n);
     if (n == 0) return 0;
+    if (in_dt == DT_F32 && out_dt == DT_BF16 && n % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 8 == 0) {
+        xielu_f32_bf16_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            (const float4*)x, params, p_dt, (uint2*)out, n / 4);
+        NN_LAUNCH_OK("xielu");
+        return 0;
+    }
     xielu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, in_dt, params, p_dt, out, out_dt, n);
     NN_LAUNCH_OK("xielu");
     return 0;

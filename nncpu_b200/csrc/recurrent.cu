@@ -6,10 +6,12 @@
 //     a_t = sigmoid(z_t)^(1/tau)                 (a decay per key channel, from the gate logits z_t)
 //     S_t = diag(a_t) S_(t-1) + k_t v_t^T
 //     o_t = S_t^T q_t
-// The columns of S do not depend on one another, so a warp owns 32 of them (a lane one column, its d
-// numbers in registers) and walks the tokens of its sequence in order; q, k and a of a token are shared by
-// the warp through shared memory.  The order of operations of a (sequence, head, column) does not depend on
-// how the sequence was cut into steps or on what else the step holds, so the results are the same bits.
+// The columns of S do not depend on one another, so a block owns a few of them, keeps them in registers and walks
+// the tokens of its sequence in order; q, k and a of a token are shared by the block through shared memory.  The
+// order of operations of a (sequence, head, column) does not depend on how the sequence was cut into steps or on
+// what else the step holds, so the results are the same bits.  Per token the recurrence costs 2 d e multiply-adds
+// a head whatever the arrangement, and 32-bit multiply-adds run on the CUDA cores, so the kernel's job is to keep
+// every SM's lanes busy with them.
 
 #include <math.h>
 
@@ -18,91 +20,167 @@
 
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
+// The decays of a prompt's tokens, made once for all the blocks that read them: z <- sigmoid(z)^(1/tau) in place.
+__global__ void gla_decay_kernel(float* __restrict__ z, long n, float inv_tau) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < n) z[idx] = expf(log_sigmoid_f(z[idx]) * inv_tau);
+}
+
+extern "C" int nncpu_gla_decay(float* z, long n, float tau, void* stream) {
+    NN_CHECK(n >= 0 && tau > 0.0f, "gla_decay: %ld elements, tau %g", n, tau);
+    if (n == 0) return 0;
+    gla_decay_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(z, n, 1.0f / tau);
+    NN_LAUNCH_OK("gla_decay");
+    return 0;
+}
+
 // proj [n_tok, row] float32 holds per token q (H*d), k (H*d), v (H*e), g (H*e); z [n_tok, H*d] float32 the
-// decay logits.  state [n_slots + 1, H, d, e]; seq_slots[s] < 0 marks a padding sequence: its rows of o are zero
+// decay logits (or, with decays_given, the decays themselves).  state [n_slots + 1, H, d, e]; seq_slots[s] < 0 marks a padding sequence: its rows of o are zero
 // and no state is touched.  o [n_tok, H*e] float32.
+//
+// A block of four warps owns 16 columns of one head's state for one sequence, a warp four of them.  A lane keeps
+// the rows i = 32 ii + lane of its warp's four columns in registers (DMAX / 32 x 4 numbers): what it reads of a
+// token from shared memory, (a, k, q) of its rows, serves four columns, and shared memory is what bounds this
+// kernel.  A lane's partial dot products of a whole group of tokens are added over the warp in one go by a
+// butterfly that halves what a lane carries while it doubles the rows that covers.  a, k, q and v of a group of tokens are
+// staged once per block in shared memory (two buffers that take turns: one barrier a group); the next group's
+// loads are issued before this group's arithmetic.
+constexpr int kScanCols = 16;       // columns of the state a block owns
+constexpr int kScanThreads = 128;
+constexpr int kScanGroup = 8;       // tokens staged at a time
+
 template <int DMAX>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(kScanThreads)
 gla_scan_kernel(const float* __restrict__ proj, int row, const float* __restrict__ z, float* __restrict__ state,
                 const int* __restrict__ seq_slots, const int* __restrict__ cu_seqlens, float* __restrict__ o, int H,
-                int d, int e, float q_scale, float inv_tau) {
-    constexpr int PER = DMAX / 32;              // key channels a lane fetches per token
-    __shared__ float4 shared[DMAX];             // (a, k, q, -) of the token under way
-    const int seq = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
-    const int j = blockIdx.z * 32 + lane;
-    const bool live = j < e;
+                int d, int e, float q_scale, float inv_tau, int decays_given) {
+    constexpr int DR = DMAX / 32;                             // rows of its columns that a lane keeps
+    constexpr int TB = DMAX <= 128 ? kScanGroup : kScanGroup / 2;   // tokens a group (shared memory: 2 TB DMAX 16 bytes)
+    constexpr int PER = TB * DMAX / kScanThreads;             // (token, key channel) pairs a thread stages
+    constexpr int N = 4 * TB;                                 // partial sums a lane carries through a group
+    __shared__ float4 shared[2][TB][DMAX];                    // (a, k, q, -) of the group under way and of the next
+    __shared__ float4 shared_v[2][TB][kScanCols / 4];         // v of the block's columns
+    const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int j0 = blockIdx.z * kScanCols + warp * 4;         // this warp's first column
     const int t0 = cu_seqlens[seq], t1 = cu_seqlens[seq + 1];
     const int slot = seq_slots[seq];
     if (slot < 0) {
-        if (live)
-            for (int t = t0; t < t1; ++t) o[(size_t)t * H * e + (size_t)h * e + j] = 0.0f;
+        if (lane < 4 && j0 + lane < e)
+            for (int t = t0; t < t1; ++t) o[(size_t)t * H * e + (size_t)h * e + j0 + lane] = 0.0f;
         return;
     }
-    float* s_col = state + (((size_t)slot * H + h) * d) * e + j;
-    float S[DMAX];
+    float* s_head = state + ((size_t)slot * H + h) * (size_t)d * e;
+    float S[DR][4];
 #pragma unroll
-    for (int i = 0; i < DMAX; ++i) S[i] = (live && i < d) ? s_col[(size_t)i * e] : 0.0f;
-
+    for (int ii = 0; ii < DR; ++ii) {
+        const int i = ii * 32 + lane;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) S[ii][c] = (i < d && j0 + c < e) ? s_head[(size_t)i * e + j0 + c] : 0.0f;
+    }
     const size_t q_at = (size_t)h * d, k_at = (size_t)H * d + (size_t)h * d, v_at = 2 * (size_t)H * d + (size_t)h * e;
+    // The tokens come in groups of TB: a group's q, k, v and decay logits are fetched into registers while the group
+    // before it is worked on, turned into (a, k, q) and put into the shared buffer that is free; one barrier a group.
     float nq[PER], nk[PER], nz[PER], nv = 0.0f;
-    auto fetch = [&](int t) {
-        const float* p = proj + (size_t)t * row;
+    const int v_tt = tid / kScanCols, v_col = tid % kScanCols;      // the v that this thread stages (TB * 16 of them)
+    auto fetch = [&](int g0) {
+        const int nt = min(TB, t1 - g0);
 #pragma unroll
         for (int c = 0; c < PER; ++c) {
-            const int i = lane + 32 * c;
-            if (i < d) {
+            const int idx = tid + kScanThreads * c;
+            const int tt = idx / DMAX, i = idx % DMAX;
+            if (tt < nt && i < d) {
+                const float* p = proj + (size_t)(g0 + tt) * row;
                 nq[c] = p[q_at + i];
                 nk[c] = p[k_at + i];
-                nz[c] = z[(size_t)t * H * d + (size_t)h * d + i];
+                nz[c] = z[(size_t)(g0 + tt) * H * d + (size_t)h * d + i];
             }
         }
-        nv = live ? p[v_at + j] : 0.0f;
+        const int col = blockIdx.z * kScanCols + v_col;
+        nv = (v_tt < TB && v_tt < nt && col < e) ? proj[(size_t)(g0 + v_tt) * row + v_at + col] : 0.0f;
     };
     if (t0 < t1) fetch(t0);
-    for (int t = t0; t < t1; ++t) {
+    int buf = 0;
+    for (int g0 = t0; g0 < t1; g0 += TB, buf ^= 1) {
+        const int nt = min(TB, t1 - g0);
 #pragma unroll
         for (int c = 0; c < PER; ++c) {
-            const int i = lane + 32 * c;
-            if (i < d) shared[i] = make_float4(expf(log_sigmoid_f(nz[c]) * inv_tau), nk[c], nq[c] * q_scale, 0.0f);
+            const int idx = tid + kScanThreads * c;
+            const int tt = idx / DMAX, i = idx % DMAX;
+            // rows beyond d hold zeros: they keep their part of the state at zero and add nothing
+            shared[buf][tt][i] = (tt < nt && i < d) ? make_float4(decays_given ? nz[c] : expf(log_sigmoid_f(nz[c]) * inv_tau),
+                                                                  nk[c], nq[c] * q_scale, 0.0f)
+                                                    : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
-        const float v = nv;
-        __syncwarp();
-        if (t + 1 < t1) fetch(t + 1);           // the next token's loads fly under this token's arithmetic
-        float acc = 0.0f;
+        if (v_tt < TB) reinterpret_cast<float*>(shared_v[buf][v_tt])[v_col] = nv;
+        __syncthreads();      // the other buffer was read before its readers came here
+        if (g0 + TB < t1) fetch(g0 + TB);
+        // the group's arithmetic first, token by token: x[4 tt + c] is this lane's part of o[tt] in column c
+        float x[N];
 #pragma unroll
-        for (int i = 0; i < DMAX; ++i) {
-            if (i < d) {
-                const float4 c = shared[i];
-                S[i] = fmaf(c.x, S[i], c.y * v);
-                acc = fmaf(S[i], c.z, acc);
+        for (int tt = 0; tt < TB; ++tt) {
+            x[4 * tt] = x[4 * tt + 1] = x[4 * tt + 2] = x[4 * tt + 3] = 0.0f;
+            if (tt < nt) {
+                const float4 v = shared_v[buf][tt][warp];
+                float4 c[DR];       // all of the token's loads first: they do not wait for one another
+#pragma unroll
+                for (int ii = 0; ii < DR; ++ii) c[ii] = shared[buf][tt][ii * 32 + lane];
+#pragma unroll
+                for (int ii = 0; ii < DR; ++ii) {
+                    S[ii][0] = fmaf(c[ii].x, S[ii][0], c[ii].y * v.x);
+                    S[ii][1] = fmaf(c[ii].x, S[ii][1], c[ii].y * v.y);
+                    S[ii][2] = fmaf(c[ii].x, S[ii][2], c[ii].y * v.z);
+                    S[ii][3] = fmaf(c[ii].x, S[ii][3], c[ii].y * v.w);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) x[4 * tt + k] = fmaf(S[ii][k], c[ii].z, x[4 * tt + k]);
+                }
             }
         }
-        if (live) o[(size_t)t * H * e + (size_t)h * e + j] = acc;
-        __syncwarp();
-    }
-    if (live) {
+        // then one sum over the warp for all of them: at every stage a lane hands half of what it carries to the
+        // lane m away and adds what it gets to the half it keeps, so that in the end lane n % N holds sum number n
+        // (N - 1 shuffles for N sums, and the shuffles of a stage do not wait for one another)
 #pragma unroll
-        for (int i = 0; i < DMAX; ++i)
-            if (i < d) s_col[(size_t)i * e] = S[i];
+        for (int m = N / 2; m >= 1; m >>= 1) {
+            const bool up = lane & m;
+#pragma unroll
+            for (int k = 0; k < m; ++k) {
+                const float got = __shfl_xor_sync(0xffffffffu, up ? x[k] : x[k + m], m);
+                x[k] = (up ? x[k + m] : x[k]) + got;
+            }
+        }
+#pragma unroll
+        for (int m = N; m < 32; m <<= 1) x[0] += __shfl_xor_sync(0xffffffffu, x[0], m);
+        {
+            const int n = lane % N, tt = n >> 2, col = j0 + (n & 3);
+            if (lane < N && tt < nt && col < e) o[(size_t)(g0 + tt) * H * e + (size_t)h * e + col] = x[0];
+        }
+    }
+#pragma unroll
+    for (int ii = 0; ii < DR; ++ii) {
+        const int i = ii * 32 + lane;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            if (i < d && j0 + c < e) s_head[(size_t)i * e + j0 + c] = S[ii][c];
     }
 }
 
 extern "C" int nncpu_gla_scan(const float* proj, int row, const float* z, float* state, const int* seq_slots,
                               const int* cu_seqlens, float* o, int n_seqs, int H, int d, int e, float q_scale,
-                              float tau, void* stream) {
+                              float tau, int decays_given, void* stream) {
     NN_CHECK(n_seqs >= 0 && H > 0 && d > 0 && e > 0, "gla_scan: %d sequences, %d heads of %d x %d", n_seqs, H, d, e);
     NN_CHECK(d <= 256, "gla_scan: %d key channels a head (at most 256)", d);
     NN_CHECK(row >= 2 * H * d + 2 * H * e, "gla_scan: rows of %d floats for %d heads of %d x %d", row, H, d, e);
     NN_CHECK(tau > 0.0f, "gla_scan: tau %g", tau);
-    NN_CHECK(H <= 65535 && (e + 31) / 32 <= 65535, "gla_scan: grid");
+    NN_CHECK(H <= 65535 && (e + kScanCols - 1) / kScanCols <= 65535, "gla_scan: grid");
     if (n_seqs == 0) return 0;
-    dim3 grid(n_seqs, H, (e + 31) / 32);
+    dim3 grid(n_seqs, H, (e + kScanCols - 1) / kScanCols);
     const float inv_tau = 1.0f / tau;
     cudaStream_t st = (cudaStream_t)stream;
-    if (d <= 32) gla_scan_kernel<32><<<grid, 32, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, e, q_scale, inv_tau);
-    else if (d <= 64) gla_scan_kernel<64><<<grid, 32, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, e, q_scale, inv_tau);
-    else if (d <= 128) gla_scan_kernel<128><<<grid, 32, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, e, q_scale, inv_tau);
-    else gla_scan_kernel<256><<<grid, 32, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, e, q_scale, inv_tau);
+    const int T = kScanThreads;
+    if (d <= 32) gla_scan_kernel<32><<<grid, T, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, e, q_scale, inv_tau, decays_given);
+    else if (d <= 64) gla_scan_kernel<64><<<grid, T, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, e, q_scale, inv_tau, decays_given);
+    else if (d <= 128) gla_scan_kernel<128><<<grid, T, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, e, q_scale, inv_tau, decays_given);
+    else gla_scan_kernel<256><<<grid, T, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, e, q_scale, inv_tau, decays_given);
     NN_LAUNCH_OK("gla_scan");
     return 0;
 }
@@ -140,5 +218,75 @@ extern "C" int nncpu_gla_output(const float* o, const float* proj, int row, int 
     gla_output_kernel<<<(unsigned)((n_items + 7) / 8), 256, 0, (cudaStream_t)stream>>>(o, proj, row, g_at, w, w_dt, eps,
                                                                                        out, out_dt, n_items, H, e);
     NN_LAUNCH_OK("gla_output");
+    return 0;
+}
+
+// One token per sequence (a decode step): recurrence, norm and gate in one launch.  A block owns a (sequence, head)
+// pair; thread j owns column j of the state and streams its d rows through once, rows being contiguous over the
+// columns, so a step reads and writes the state at full width and nothing of it stays in registers.  The decays, k
+// and q of the token are shared through shared memory; the head's sum of squares is a block sum.  A negative slot
+// (padding) gives zeros and touches no state.  Threads: e rounded up to a warp (e <= 1024).
+__global__ void __launch_bounds__(1024)
+gla_step_kernel(const float* __restrict__ proj, int row, const float* __restrict__ z, float* __restrict__ state,
+                const int* __restrict__ seq_slots, const void* __restrict__ w, int w_dt, float eps,
+                void* __restrict__ out, int out_dt, int H, int d, int e, float q_scale, float inv_tau) {
+    extern __shared__ float4 akq[];          // d entries of (a, k, q, -)
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
+    const int slot = seq_slots[t];
+    const size_t out_at = (size_t)t * H * e + (size_t)h * e + j;
+    if (slot < 0) {
+        if (j < e) st_f(out, out_at, out_dt, 0.0f);
+        return;
+    }
+    const float* p = proj + (size_t)t * row;
+    for (int i = j; i < d; i += blockDim.x)
+        akq[i] = make_float4(expf(log_sigmoid_f(z[(size_t)t * H * d + (size_t)h * d + i]) * inv_tau),
+                             p[(size_t)H * d + (size_t)h * d + i], p[(size_t)h * d + i] * q_scale, 0.0f);
+    __syncthreads();
+    float acc = 0.0f;
+    if (j < e) {
+        const float v = p[2 * (size_t)H * d + (size_t)h * e + j];
+        float* col = state + (((size_t)slot * H + h) * d) * e + j;
+        int i = 0;
+        for (; i + 8 <= d; i += 8) {         // eight rows in flight (32 were slower at every batch size measured)
+            float s[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) s[u] = col[(size_t)(i + u) * e];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float4 c = akq[i + u];
+                s[u] = fmaf(c.x, s[u], c.y * v);
+                acc = fmaf(s[u], c.z, acc);
+                col[(size_t)(i + u) * e] = s[u];
+            }
+        }
+        for (; i < d; ++i) {
+            const float4 c = akq[i];
+            const float s = fmaf(c.x, col[(size_t)i * e], c.y * v);
+            acc = fmaf(s, c.z, acc);
+            col[(size_t)i * e] = s;
+        }
+    }
+    const float ss = block_sum(j < e ? acc * acc : 0.0f, scratch);
+    if (j < e) {
+        const float scale = 1.0f / sqrtf(ss * (1.0f / (float)e) + eps);
+        const float gate = p[2 * (size_t)H * d + (size_t)H * e + (size_t)h * e + j];
+        st_f(out, out_at, out_dt, ((acc * scale) * ld_f(w, j, w_dt)) * (gate / (1.0f + expf(-gate))));
+    }
+}
+
+extern "C" int nncpu_gla_step(const float* proj, int row, const float* z, float* state, const int* seq_slots,
+                              const void* w, int w_dt, float eps, void* out, int out_dt, int n_tok, int H, int d, int e,
+                              float q_scale, float tau, void* stream) {
+    NN_CHECK(n_tok >= 0 && H > 0 && H <= 65535 && d > 0 && e > 0, "gla_step: %d tokens, %d heads of %d x %d", n_tok, H, d, e);
+    NN_CHECK(e <= 1024, "gla_step: %d value channels a head (at most 1024)", e);
+    NN_CHECK(d <= 2048, "gla_step: %d key channels a head (at most 2048)", d);
+    NN_CHECK(row >= 2 * H * d + 2 * H * e && tau > 0.0f, "gla_step: rows of %d floats, tau %g", row, tau);
+    if (n_tok == 0) return 0;
+    const int threads = (e + 31) / 32 * 32;
+    gla_step_kernel<<<dim3(n_tok, H), threads, (size_t)d * sizeof(float4), (cudaStream_t)stream>>>(
+        proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau);
+    NN_LAUNCH_OK("gla_step");
     return 0;
 }

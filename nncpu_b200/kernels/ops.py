@@ -146,6 +146,20 @@ def rmsnorm(x, gamma, eps: float, out, rows=None, gamma_offset: float = 0.0, acc
           _i(_code(out)), _ptr(rows), _i(n_rows), _i(dim), _f(eps), _f(gamma_offset), _i(accumulate), _stream())
 
 
+def rmsnorm_pair_supported(dim: int) -> bool:
+    return dim > 0 and dim % 4 == 0 and dim <= 8192
+
+
+def rmsnorm_pair(branch, residual, gamma1, offset1: float, eps1: float, gamma2, offset2: float, eps2: float, out) -> None:
+    """residual += rmsnorm(branch) * (gamma1 + offset1), then out = rmsnorm(residual) * (gamma2 + offset2): the norm
+    that closes a sublayer and the one that opens the next in one pass.  branch and residual float32 [n, dim]."""
+    n, dim = residual.shape
+    assert branch.shape == residual.shape == out.shape and branch.dtype == residual.dtype == torch.float32
+    assert gamma1.numel() == gamma2.numel() == dim and gamma1.dtype == gamma2.dtype
+    _call("generic", "nncpu_rmsnorm_pair", _ptr(branch), _ptr(residual), _ptr(gamma1), _f(offset1), _f(eps1), _ptr(gamma2),
+          _f(offset2), _f(eps2), _i(_code(gamma1)), _ptr(out), _i(_code(out)), _i(n), _i(dim), _stream())
+
+
 def linear_simt(x, w, bias, out, accumulate: bool = False) -> None:
     """out (+)= x . w^T + bias on CUDA cores in 32-bit; any sizes and element types."""
     m, k = x.shape
@@ -479,11 +493,32 @@ def softcap(x, cap: float) -> None:
     _call("generic", "nncpu_softcap", _ptr(x), ctypes.c_long(x.numel()), _f(cap), _stream())
 
 
-def gla_scan(proj, z, state, seq_slots, cu_seqlens, o, n_seqs: int, n_heads: int, d: int, e: int, q_scale: float,
+def gla_decay(z, tau: float) -> None:
+    """z <- sigmoid(z)^(1/tau) in place (float32): the decays of gated linear attention from their logits."""
+    assert z.dtype == torch.float32 and z.is_contiguous()
+    _call("recurrent", "nncpu_gla_decay", _ptr(z), ctypes.c_long(z.numel()), _f(tau), _stream())
+
+
+def gla_step(proj, z, state, seq_slots, weight, eps: float, out, n_heads: int, d: int, e: int, q_scale: float,
              tau: float) -> None:
+    """A decode step of gated linear attention, one token per sequence: the recurrence on ``state`` (as ``gla_scan``
+    with sequences of one token, ``z`` holding logits), then the heads' norm, weight and gate (as ``gla_output``),
+    in one launch.  ``out`` [n, H e] in float32 or bfloat16."""
+    n = out.shape[0]
+    assert proj.dtype == z.dtype == state.dtype == torch.float32
+    assert proj.shape == (n, 2 * n_heads * (d + e)) and z.shape == (n, n_heads * d) and out.shape == (n, n_heads * e)
+    assert state.shape[1:] == (n_heads, d, e) and state.is_contiguous() and proj.is_contiguous() and weight.numel() == e
+    assert seq_slots.dtype == torch.int32 and seq_slots.numel() >= n
+    _call("recurrent", "nncpu_gla_step", _ptr(proj), _i(proj.shape[1]), _ptr(z), _ptr(state), _ptr(seq_slots),
+          _ptr(weight), _i(_code(weight)), _f(eps), _ptr(out), _i(_code(out)), _i(n), _i(n_heads), _i(d), _i(e),
+          _f(q_scale), _f(tau), _stream())
+
+
+def gla_scan(proj, z, state, seq_slots, cu_seqlens, o, n_seqs: int, n_heads: int, d: int, e: int, q_scale: float,
+             tau: float, decays_given: bool = False) -> None:
     """Gated linear attention's recurrence over the step's tokens, sequence by sequence in order.  ``proj``
     float32 [n, 2 H d + 2 H e] holds q, k, v and the output gate per token, ``z`` float32 [n, H d] the decay
-    logits; ``state`` float32 [slots, H, d, e] is read and left updated for the slots in ``seq_slots`` (a negative
+    logits (with ``decays_given`` the decays themselves, as ``gla_decay`` leaves them); ``state`` float32 [slots, H, d, e] is read and left updated for the slots in ``seq_slots`` (a negative
     slot: a padding sequence, zeros out); ``o`` float32 [n, H e] receives S_t^T q_t."""
     n = o.shape[0]
     assert proj.dtype == z.dtype == state.dtype == o.dtype == torch.float32
@@ -491,7 +526,8 @@ def gla_scan(proj, z, state, seq_slots, cu_seqlens, o, n_seqs: int, n_heads: int
     assert state.shape[1:] == (n_heads, d, e) and state.is_contiguous() and proj.is_contiguous()
     assert seq_slots.dtype == torch.int32 and cu_seqlens.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1
     _call("recurrent", "nncpu_gla_scan", _ptr(proj), _i(proj.shape[1]), _ptr(z), _ptr(state), _ptr(seq_slots),
-          _ptr(cu_seqlens), _ptr(o), _i(n_seqs), _i(n_heads), _i(d), _i(e), _f(q_scale), _f(tau), _stream())
+          _ptr(cu_seqlens), _ptr(o), _i(n_seqs), _i(n_heads), _i(d), _i(e), _f(q_scale), _f(tau), _i(decays_given),
+          _stream())
 
 
 def gla_output(o, proj, weight, eps: float, out, n_heads: int, d: int, e: int) -> None:

@@ -150,7 +150,8 @@ class Attention(Mixer):
                     self._attend(ctx, q, cache, attn)
         with rt.phase("attn_out", self.w_o, n):
             # the last write into the residual stream: it may leave the next norm its input
-            rt.linear(attn, self.w_o, self.b_o, residual, accumulate=True, then_norm=getattr(ctx, "next_norm", None))
+            rt.linear(attn, self.w_o, self.b_o, residual, accumulate=not getattr(ctx, "branch_is_fresh", False),
+                      then_norm=getattr(ctx, "next_norm", None))
 
     def _core_phase(self, ctx, cache):
         """The profiler's scope of the attention itself: every token streams the keys and values of its span

@@ -74,6 +74,10 @@ class NormRequest:
     eps: float
     size: int
     result: Optional["DeferredNorm"] = None
+    # A block that norms its own output ("sandwich") can run this norm in the same pass as its closing norm; a
+    # requester that sets ``wants_output`` finds the norm's finished output in ``output`` then.
+    wants_output: bool = False
+    output: Optional[torch.Tensor] = None
 
 
 @dataclass

@@ -5,8 +5,11 @@ The residual stream stays in float32 from the embedding to the final norm.
 """
 from __future__ import annotations
 
+import torch
+
+from ..kernels import ops
 from . import base
-from .base import Block, register_block
+from .base import Block, NormRequest, register_block
 
 
 @register_block("prenorm")
@@ -68,8 +71,8 @@ class PreNormBlock(Block):
 class SandwichBlock(Block):
     """A norm before and after each sublayer: x += norm1_post(mixer(norm1(x))), then, if the layer has a
     feed-forward, x += norm2_post(feed_forward(norm2(x))).  A sublayer writes its output into a float32 branch
-    of its own (the parts add into what they are given, so the branch starts at zero), and the closing norm adds
-    its result into the residual stream."""
+    of its own, and the closing norm adds its result into the residual stream; the norm that opens whatever follows
+    (the block's own feed-forward, or the next block when it is of this kind too) runs in the same pass."""
 
     def __init__(self, spec, reads_other_cache: bool = False):
         kwargs = {"reads_other_cache": True} if reads_other_cache else {}
@@ -98,20 +101,72 @@ class SandwichBlock(Block):
     def cache_requests(self):
         return [(self.mixer.kv_request(), self.mixer.state_request())]
 
-    def _sublayer(self, ctx, norm, run, norm_post, residual):
-        rt = self.rt
-        with rt.scope():
-            x = norm.forward(ctx, residual)
-            branch = rt.empty(*residual.shape, dtype=residual.dtype)
-            if not branch.is_meta:
-                branch.zero_()
+    def entry_norm_request(self, ctx, residual):
+        n = self.norm1
+        return NormRequest(n, residual, n.gamma, n.eps, n.size, wants_output=True)
+
+    def _close(self, ctx, norm_post, branch, residual, then, out):
+        """residual += norm_post(branch); and, in the same pass where the sizes allow it, ``out`` = then(residual), the
+        norm that opens what follows.  Returns whether ``out`` was written."""
+        if (then is not None and out is not None and hasattr(then, "offset") and then.size == norm_post.size
+                and then.gamma.dtype == norm_post.gamma.dtype and ops.rmsnorm_pair_supported(then.size)
+                and residual.dtype == torch.float32):
+            with self.rt.phase("norm"):
+                ops.rmsnorm_pair(branch, residual, norm_post.gamma, norm_post.offset, norm_post.eps, then.gamma,
+                                 then.offset, then.eps, out)
+            return True
+        norm_post.add_into(ctx, branch, residual)
+        return False
+
+    def _branch(self, ctx, residual, run, x):
+        """A sublayer's output in a branch of its own.  The parts add into what they are given; told that the branch
+        is fresh, their last product writes instead, which saves clearing it."""
+        branch = self.rt.empty(*residual.shape, dtype=residual.dtype)
+        ctx.branch_is_fresh = True
+        try:
             run(x, branch)
-            norm_post.add_into(ctx, branch, residual)
+        finally:
+            ctx.branch_is_fresh = False
+        return branch
+
+    def _next_input(self, ctx, residual):
+        """Where the first norm of the block that follows is left: two buffers of the step take turns."""
+        turn = ctx.memo.get("sandwich_turn", 0)
+        ctx.memo["sandwich_turn"] = 1 - turn
+        key = ("sandwich_x", turn)
+        buf = ctx.memo.get(key)
+        if buf is None:
+            buf = ctx.memo[key] = self.rt.empty(*residual.shape, keep=True)
+        return buf
 
     def forward(self, ctx, residual, caches):
+        rt = self.rt
+        handed, after = ctx.next_norm, ctx.after_block
         ctx.next_norm = ctx.after_block = None      # these norms do not ride on the products around them
-        self._sublayer(ctx, self.norm1, lambda x, out: self.mixer.forward(ctx, x, out, caches[0]), self.norm1_post,
-                       residual)
-        if self.feed_forward is not None:
-            self._sublayer(ctx, self.norm2, lambda x, out: self.feed_forward.forward(ctx, x, out), self.norm2_post,
-                           residual)
+        wanted = after if (after is not None and after.wants_output) else None
+        nxt = self._next_input(ctx, residual) if wanted is not None else None
+        ff = self.feed_forward
+        with rt.scope():
+            x2 = rt.empty(*residual.shape) if ff is not None else None      # outlives the mixer's temporaries
+            with rt.scope():
+                if handed is not None and handed.norm is self.norm1 and handed.output is not None:
+                    x = handed.output               # the block before left it with its closing norm
+                else:
+                    x = self.norm1.forward(ctx, residual)
+                branch = self._branch(ctx, residual, lambda x, out: self.mixer.forward(ctx, x, out, caches[0]), x)
+                if ff is not None:
+                    if not self._close(ctx, self.norm1_post, branch, residual, self.norm2, x2):
+                        x2 = None
+                elif wanted is not None and self._close(ctx, self.norm1_post, branch, residual, wanted.norm, nxt):
+                    wanted.output = nxt
+                else:
+                    self._close(ctx, self.norm1_post, branch, residual, None, None)
+            if ff is not None:
+                with rt.scope():
+                    x = x2 if x2 is not None else self.norm2.forward(ctx, residual)
+                    branch = self._branch(ctx, residual, lambda x, out: ff.forward(ctx, x, out), x)
+                    if wanted is not None and self._close(ctx, self.norm2_post, branch, residual, wanted.norm, nxt):
+                        wanted.output = nxt
+                    else:
+                        self._close(ctx, self.norm2_post, branch, residual, None, None)
+        ctx.next_norm = after       # the block that follows finds its request there, fulfilled or not

@@ -12,8 +12,9 @@ With h the mixer's input, per head (d = key_dim, e = value_dim):
 The four projections of h are one product (their rows stacked); products run in the run's element type with
 32-bit accumulators and their results stay in float32; the decay (its logarithm and exponential), the
 recurrence and the norm are 32-bit in both run types.  The recurrence walks a sequence's tokens in order inside
-one kernel, so a prompt cut into several steps, a batch of unequal sequences and token-by-token decoding all
-give the same bits.
+one kernel, so a prompt cut into portions and a batch of unequal sequences give the same bits; a decode step
+(one token per sequence) runs a kernel of its own that streams the state once and adds a column's terms in
+another order, which differs by rounding in the last bits.
 """
 from __future__ import annotations
 
@@ -81,14 +82,22 @@ class GatedLinearAttention(Mixer):
         with rt.phase("gla_decay", self.w_a1, n):
             rt.linear(x, self.w_a1, None, low)
             rt.linear(low, self.w_a2, self.b_a2, z)
-        o = rt.empty(n, self.v_size, dtype=torch.float32)
-        with rt.phase("gla_scan", nbytes=4.0 * (proj.numel() + z.numel() + o.numel())
-                      + 8.0 * ctx.n_seqs * s.n_heads * s.key_dim * s.value_dim,
-                      flops=4.0 * n * s.n_heads * s.key_dim * s.value_dim):
-            ops.gla_scan(proj, z, cache.state, ctx.seq_slots, ctx.cu_seqlens, o, ctx.n_seqs, s.n_heads, s.key_dim,
-                         s.value_dim, s.key_dim ** -0.5, s.tau)
         gated = rt.empty(n, self.v_size)
-        with rt.phase("gla_gate"):
-            ops.gla_output(o, proj, self.w_norm, s.eps, gated, s.n_heads, s.key_dim, s.value_dim)
+        state_bytes = 8.0 * ctx.n_seqs * s.n_heads * s.key_dim * s.value_dim       # read and written once a step
+        if ctx.is_decode and s.value_dim <= 1024:
+            # one token per sequence: recurrence, norm and gate in one launch that streams the state once
+            with rt.phase("gla_scan", nbytes=state_bytes + 4.0 * (proj.numel() + z.numel()) + gated.numel() * gated.element_size()):
+                ops.gla_step(proj, z, cache.state, ctx.seq_slots, self.w_norm, s.eps, gated, s.n_heads, s.key_dim,
+                             s.value_dim, s.key_dim ** -0.5, s.tau)
+        else:
+            o = rt.empty(n, self.v_size, dtype=torch.float32)
+            with rt.phase("gla_decay"):
+                ops.gla_decay(z, s.tau)         # once for all the blocks of the scan that read a token's decays
+            with rt.phase("gla_scan", nbytes=state_bytes + 4.0 * (proj.numel() + z.numel() + o.numel()),
+                          flops=4.0 * n * s.n_heads * s.key_dim * s.value_dim):
+                ops.gla_scan(proj, z, cache.state, ctx.seq_slots, ctx.cu_seqlens, o, ctx.n_seqs, s.n_heads, s.key_dim,
+                             s.value_dim, s.key_dim ** -0.5, s.tau, decays_given=True)
+            with rt.phase("gla_gate"):
+                ops.gla_output(o, proj, self.w_norm, s.eps, gated, s.n_heads, s.key_dim, s.value_dim)
         with rt.phase("gla_out", self.w_o, n):
-            rt.linear(gated, self.w_o, None, residual, accumulate=True)
+            rt.linear(gated, self.w_o, None, residual, accumulate=not getattr(ctx, "branch_is_fresh", False))

@@ -103,4 +103,4 @@ class DenseMlp(FeedForward):
         with rt.phase("ffn_act"):
             ops.xielu(up, self.act, act)
         with rt.phase("ffn_down", self.w_down, n):
-            rt.linear(act, self.w_down, self.b_down, residual, accumulate=True)
+            rt.linear(act, self.w_down, self.b_down, residual, accumulate=not getattr(ctx, "branch_is_fresh", False))

@@ -99,6 +99,21 @@ def test_norm_with_weights_around_zero_and_added_into_the_stream():
     check(stream, want, 1e-6, "norm added into the stream")
 
 
+@pytest.mark.parametrize("dim", [88, 320, 1024, 2052, 8192])
+def test_closing_and_opening_norm_in_one_pass(dim):
+    """r += norm(b) * (1 + w1); y = norm(r) * (1 + w2) against the two norms one after the other."""
+    g = torch.Generator().manual_seed(dim)
+    b, r = torch.randn(5, dim, generator=g) * 2, torch.randn(5, dim, generator=g)
+    w1, w2 = torch.randn(dim, generator=g) * 0.1, torch.randn(dim, generator=g) * 0.1
+    want_r = r.double().numpy() + P.offset_norm(b.double().numpy(), w1.double().numpy(), 1e-6)
+    want_y = P.offset_norm(want_r, w2.double().numpy(), 3e-6)
+    for out_dt in (torch.float32, torch.bfloat16):
+        stream, y = r.to(DEV), torch.empty(5, dim, dtype=out_dt, device=DEV)
+        ops.rmsnorm_pair(b.to(DEV), stream, w1.to(DEV), 1.0, 1e-6, w2.to(DEV), 1.0, 3e-6, y)
+        check(stream, want_r, 1e-6, "the stream after the closing norm")
+        check(y, want_y, 2e-6 if out_dt == torch.float32 else 1e-2, "the opening norm")
+
+
 def test_xielu_both_branches_and_soft_cap():
     z = torch.linspace(-9, 9, 1001)
     for p, q in ((0.3, -0.7), (-2.0, 1.5)):
@@ -181,6 +196,27 @@ def test_gla_recurrence_alone_in_portions_and_batches(H, d, e):
     at = 0
     for b in range(3):
         assert torch.equal(torch.cat(outs[b]), whole[at:at + lens[b]]), "portions give other bits than the whole"
+        at += lens[b]
+    # the decode step's kernel (recurrence, norm and gate in one launch) against the scan followed by the output stage
+    w = torch.randn(e, generator=g).to(DEV)
+    for out_dt in (torch.float32, torch.bfloat16):
+        state.zero_()
+        state2 = torch.zeros_like(state)
+        for t in range(5):
+            proj = torch.cat([data[b][0][t:t + 1] for b in range(3)] + [data[0][0][:1]]).to(DEV)
+            z = torch.cat([data[b][1][t:t + 1] for b in range(3)] + [data[0][1][:1]]).to(DEV)
+            sl = torch.tensor(slots + [-1], dtype=torch.int32, device=DEV)
+            got = torch.empty(4, H * e, dtype=out_dt, device=DEV)
+            ops.gla_step(proj, z, state, sl, w, 1e-5, got, H, d, e, d ** -0.5, tau)
+            o = torch.empty(4, H * e, device=DEV)
+            ops.gla_scan(proj, z, state2, sl, torch.arange(5, dtype=torch.int32, device=DEV), o, 4, H, d, e, d ** -0.5, tau)
+            want = torch.empty(4, H * e, dtype=out_dt, device=DEV)
+            ops.gla_output(o, proj, w, 1e-5, want, H, d, e)
+            check(got[:3], want[:3], 1e-5 if out_dt == torch.float32 else 1e-2, f"decode step {t}")
+            assert float(got[3].float().abs().max()) == 0, "a padding row is not zero"
+        check(state, state2, 1e-6, "the state after five decode steps")
+    at = 0
+    for b in range(3):
         at += lens[b]
     assert float(state[n_slots].abs().max()) == 0 and float(state[1].abs().max()) == 0, "a foreign state row was written"
 
