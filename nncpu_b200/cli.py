@@ -131,7 +131,7 @@ def parse_options(argv: List[str]) -> Options:
 
 
 def usage(argv0: str = "nncpu-b200") -> str:
-    return f"""nncpu-b200 {__version__} - run Qwen3 models on one B200
+    return f"""nncpu-b200 {__version__} - run Qwen3 and Romepel models on one B200
 
 usage: {argv0} -m DIR --tokens "ID ID ..."   continue the token ids and exit
        {argv0} -m DIR -p TEXT                answer one message and exit (needs tokenizer.json in DIR)
@@ -392,16 +392,21 @@ def run_info(o: Options, out=sys.stdout) -> int:
     files, where, label = open_checkpoint(o.args[0])
     try:
         check_tensors({n: files[name].shape(n) for n, name in where.items()}, params, label)
+    except Exception:
+        for f in files.values():
+            f.close()
+        raise
+    n = 0
+    try:
+        for p in params:
+            if p.name in where:
+                c = 1
+                for s in files[where[p.name]].shape(p.name):      # the file's own sizes: a part may leave one to it
+                    c *= s
+                n += c
     finally:
         for f in files.values():
             f.close()
-    n = 0
-    for p in params:
-        if p.name in where:
-            c = 1
-            for s in p.shape:
-                c *= s
-            n += c
     out.write(json.dumps({"config": cfg.to_dict(), "tensors": len(where), "parameters": n}, indent=2) + "\n")
     return 0
 

@@ -60,6 +60,7 @@ struct AttnParams {
     int n_seqs, n_heads, n_kv;
     float scale2;   // softmax scale times log2(e)
     int window;
+    float slope_base;   // b != 0: head h takes 2^(-b (h + 1) / n_heads) * (query position - key position) off its scaled scores
     int* status;
 };
 
@@ -335,6 +336,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const int lim_hi = row < n_rows ? pos0 + row : -1;
         const int lim_lo = (p.window > 0 && lim_hi + 1 > p.window) ? lim_hi + 1 - p.window : 0;
         const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(t * kStreamCols);
+        // the distance bias in the unit of the unscaled scores (the scale is applied with the reference maximum)
+        const float bias_per_key = p.slope_base != 0.0f
+            ? exp2f(-p.slope_base * (float)(h + 1) / (float)p.n_heads) * 1.4426950408889634f / p.scale2 : 0.0f;
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = t < n_streams;   // the second warpgroup of a block with one head has nothing to do
         for (int i = 0; ok && i < n_steps; ++i) {
@@ -357,6 +361,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             auto load_half = [&](int hf, uint32_t (&u)[64]) {
                 tmem_ld64(tmem_row + (uint32_t)(64 * hf), u);
                 const int kb = k_base + 64 * hf;
+                if (bias_per_key != 0.0f) {
+                    const float far = (float)(lim_hi - kb);     // the distance of the page's first key
+#pragma unroll
+                    for (int c = 0; c < 64; ++c)
+                        u[c] = __float_as_uint(fmaf(bias_per_key, (float)c - far, __uint_as_float(u[c])));
+                }
                 if (!(kb >= lim_lo && kb + 63 <= lim_hi)) {
                     // the page crosses this row's limits
 #pragma unroll
@@ -547,7 +557,8 @@ extern "C" int nncpu_attention_prefill_tc_supported(int n_heads, int n_kv, int h
 extern "C" int nncpu_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, int n_pages,
                                           const int* block_table, int bt_stride, const int* cu_seqlens,
                                           const int* tok_pos, void* out, int n_tok, int n_seqs, int n_heads, int n_kv,
-                                          int head_dim, float scale, int window, int* status, void* stream_) {
+                                          int head_dim, float scale, int window, float slope_base, int* status,
+                                          void* stream_) {
     NN_CHECK(nncpu_attention_prefill_tc_supported(n_heads, n_kv, head_dim),
              "attention (tensor cores): head size %d with %d heads over %d key/value heads is not supported "
              "(head size 64 or 128, heads a multiple of key/value heads)", head_dim, n_heads, n_kv);
@@ -572,6 +583,7 @@ extern "C" int nncpu_attention_prefill_tc(const void* q, const void* k_pages, co
     p.n_kv = n_kv;
     p.scale2 = scale * 1.4426950408889634f;
     p.window = window;
+    p.slope_base = slope_base;
     p.status = status;
     cudaStream_t stream = (cudaStream_t)stream_;
     // two heads to a block where a key/value head has two to give; one head per block otherwise

@@ -46,37 +46,40 @@ extern "C" int nncpu_gla_decay(float* z, long n, float tau, void* stream) {
 // staged once per block in shared memory (two buffers that take turns: one barrier a group); the next group's
 // loads are issued before this group's arithmetic.
 constexpr int kScanCols = 16;       // columns of the state a block owns
-constexpr int kScanThreads = 128;
 constexpr int kScanGroup = 8;       // tokens staged at a time
 
-template <int DMAX>
-__global__ void __launch_bounds__(kScanThreads)
+// CPL columns a lane: 4 (four warps a block) where there are blocks enough to fill the GPU several times over, 2
+// (eight warps a block, twice the warps for the same state) where there are not: a warp's token is a chain of
+// dependent instructions, and an SM needs warps to put into one another's waits.
+template <int DMAX, int CPL>
+__global__ void __launch_bounds__(32 * kScanCols / CPL)
 gla_scan_kernel(const float* __restrict__ proj, int row, const float* __restrict__ z, float* __restrict__ state,
                 const int* __restrict__ seq_slots, const int* __restrict__ cu_seqlens, float* __restrict__ o, int H,
                 int d, int e, float q_scale, float inv_tau, int decays_given) {
     constexpr int DR = DMAX / 32;                             // rows of its columns that a lane keeps
     constexpr int TB = DMAX <= 128 ? kScanGroup : kScanGroup / 2;   // tokens a group (shared memory: 2 TB DMAX 16 bytes)
+    constexpr int kScanThreads = 32 * kScanCols / CPL;
     constexpr int PER = TB * DMAX / kScanThreads;             // (token, key channel) pairs a thread stages
-    constexpr int N = 4 * TB;                                 // partial sums a lane carries through a group
+    constexpr int N = CPL * TB;                               // partial sums a lane carries through a group
     __shared__ float4 shared[2][TB][DMAX];                    // (a, k, q, -) of the group under way and of the next
-    __shared__ float4 shared_v[2][TB][kScanCols / 4];         // v of the block's columns
+    __shared__ float shared_v[2][TB][kScanCols];              // v of the block's columns
     const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
-    const int j0 = blockIdx.z * kScanCols + warp * 4;         // this warp's first column
+    const int j0 = blockIdx.z * kScanCols + warp * CPL;       // this warp's first column
     const int t0 = cu_seqlens[seq], t1 = cu_seqlens[seq + 1];
     const int slot = seq_slots[seq];
     if (slot < 0) {
-        if (lane < 4 && j0 + lane < e)
+        if (lane < CPL && j0 + lane < e)
             for (int t = t0; t < t1; ++t) o[(size_t)t * H * e + (size_t)h * e + j0 + lane] = 0.0f;
         return;
     }
     float* s_head = state + ((size_t)slot * H + h) * (size_t)d * e;
-    float S[DR][4];
+    float S[DR][CPL];
 #pragma unroll
     for (int ii = 0; ii < DR; ++ii) {
         const int i = ii * 32 + lane;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) S[ii][c] = (i < d && j0 + c < e) ? s_head[(size_t)i * e + j0 + c] : 0.0f;
+        for (int c = 0; c < CPL; ++c) S[ii][c] = (i < d && j0 + c < e) ? s_head[(size_t)i * e + j0 + c] : 0.0f;
     }
     const size_t q_at = (size_t)h * d, k_at = (size_t)H * d + (size_t)h * d, v_at = 2 * (size_t)H * d + (size_t)h * e;
     // The tokens come in groups of TB: a group's q, k, v and decay logits are fetched into registers while the group
@@ -97,7 +100,7 @@ gla_scan_kernel(const float* __restrict__ proj, int row, const float* __restrict
             }
         }
         const int col = blockIdx.z * kScanCols + v_col;
-        nv = (v_tt < TB && v_tt < nt && col < e) ? proj[(size_t)(g0 + v_tt) * row + v_at + col] : 0.0f;
+        nv = (tid < TB * kScanCols && v_tt < nt && col < e) ? proj[(size_t)(g0 + v_tt) * row + v_at + col] : 0.0f;
     };
     if (t0 < t1) fetch(t0);
     int buf = 0;
@@ -112,27 +115,29 @@ gla_scan_kernel(const float* __restrict__ proj, int row, const float* __restrict
                                                                   nk[c], nq[c] * q_scale, 0.0f)
                                                     : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
-        if (v_tt < TB) reinterpret_cast<float*>(shared_v[buf][v_tt])[v_col] = nv;
+        if (tid < TB * kScanCols) shared_v[buf][v_tt][v_col] = nv;
         __syncthreads();      // the other buffer was read before its readers came here
         if (g0 + TB < t1) fetch(g0 + TB);
         // the group's arithmetic first, token by token: x[4 tt + c] is this lane's part of o[tt] in column c
         float x[N];
 #pragma unroll
         for (int tt = 0; tt < TB; ++tt) {
-            x[4 * tt] = x[4 * tt + 1] = x[4 * tt + 2] = x[4 * tt + 3] = 0.0f;
+#pragma unroll
+            for (int k = 0; k < CPL; ++k) x[CPL * tt + k] = 0.0f;
             if (tt < nt) {
-                const float4 v = shared_v[buf][tt][warp];
+                float v[CPL];
+#pragma unroll
+                for (int k = 0; k < CPL; ++k) v[k] = shared_v[buf][tt][warp * CPL + k];
                 float4 c[DR];       // all of the token's loads first: they do not wait for one another
 #pragma unroll
                 for (int ii = 0; ii < DR; ++ii) c[ii] = shared[buf][tt][ii * 32 + lane];
 #pragma unroll
                 for (int ii = 0; ii < DR; ++ii) {
-                    S[ii][0] = fmaf(c[ii].x, S[ii][0], c[ii].y * v.x);
-                    S[ii][1] = fmaf(c[ii].x, S[ii][1], c[ii].y * v.y);
-                    S[ii][2] = fmaf(c[ii].x, S[ii][2], c[ii].y * v.z);
-                    S[ii][3] = fmaf(c[ii].x, S[ii][3], c[ii].y * v.w);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) x[4 * tt + k] = fmaf(S[ii][k], c[ii].z, x[4 * tt + k]);
+                    for (int k = 0; k < CPL; ++k) {
+                        S[ii][k] = fmaf(c[ii].x, S[ii][k], c[ii].y * v[k]);
+                        x[CPL * tt + k] = fmaf(S[ii][k], c[ii].z, x[CPL * tt + k]);
+                    }
                 }
             }
         }
@@ -151,7 +156,7 @@ gla_scan_kernel(const float* __restrict__ proj, int row, const float* __restrict
 #pragma unroll
         for (int m = N; m < 32; m <<= 1) x[0] += __shfl_xor_sync(0xffffffffu, x[0], m);
         {
-            const int n = lane % N, tt = n >> 2, col = j0 + (n & 3);
+            const int n = lane % N, tt = n / CPL, col = j0 + n % CPL;
             if (lane < N && tt < nt && col < e) o[(size_t)(g0 + tt) * H * e + (size_t)h * e + col] = x[0];
         }
     }
@@ -159,10 +164,13 @@ gla_scan_kernel(const float* __restrict__ proj, int row, const float* __restrict
     for (int ii = 0; ii < DR; ++ii) {
         const int i = ii * 32 + lane;
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < CPL; ++c)
             if (i < d && j0 + c < e) s_head[(size_t)i * e + j0 + c] = S[ii][c];
     }
 }
+
+static int g_scan_cpl = 0;     // 0: by the grid's size; 2 or 4: forced (measurements and tests)
+extern "C" void nncpu_gla_scan_force_columns(int cpl) { g_scan_cpl = (cpl == 2 || cpl == 4) ? cpl : 0; }
 
 extern "C" int nncpu_gla_scan(const float* proj, int row, const float* z, float* state, const int* seq_slots,
                               const int* cu_seqlens, float* o, int n_seqs, int H, int d, int e, float q_scale,
@@ -176,11 +184,27 @@ extern "C" int nncpu_gla_scan(const float* proj, int row, const float* z, float*
     dim3 grid(n_seqs, H, (e + kScanCols - 1) / kScanCols);
     const float inv_tau = 1.0f / tau;
     cudaStream_t st = (cudaStream_t)stream;
-    const int T = kScanThreads;
-    if (d <= 32) gla_scan_kernel<32><<<grid, T, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, e, q_scale, inv_tau, decays_given);
-    else if (d <= 64) gla_scan_kernel<64><<<grid, T, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, e, q_scale, inv_tau, decays_given);
-    else if (d <= 128) gla_scan_kernel<128><<<grid, T, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, e, q_scale, inv_tau, decays_given);
-    else gla_scan_kernel<256><<<grid, T, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, e, q_scale, inv_tau, decays_given);
+    int sms = 148;
+    {
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const long blocks = (long)grid.x * grid.y * grid.z;
+    const bool narrow = g_scan_cpl == 2 || (g_scan_cpl == 0 && blocks < 4L * sms);
+#define NN_SCAN(DMAX)                                                                                               \
+    do {                                                                                                            \
+        if (narrow)                                                                                                 \
+            gla_scan_kernel<DMAX, 2><<<grid, 32 * kScanCols / 2, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, \
+                                                                          e, q_scale, inv_tau, decays_given);      \
+        else                                                                                                        \
+            gla_scan_kernel<DMAX, 4><<<grid, 32 * kScanCols / 4, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, \
+                                                                          e, q_scale, inv_tau, decays_given);      \
+    } while (0)
+    if (d <= 32) NN_SCAN(32);
+    else if (d <= 64) NN_SCAN(64);
+    else if (d <= 128) NN_SCAN(128);
+    else NN_SCAN(256);
+#undef NN_SCAN
     NN_LAUNCH_OK("gla_scan");
     return 0;
 }

@@ -458,9 +458,10 @@ def attention_prefill_tc_supported(n_heads: int, n_kv: int, head_dim: int, *tens
 
 
 def attention_prefill_tc(q, k_pages, v_pages, block_table, cu_seqlens, tok_pos, out, status, n_seqs: int,
-                         n_heads: int, n_kv: int, head_dim: int, scale: float, window: int) -> None:
+                         n_heads: int, n_kv: int, head_dim: int, scale: float, window: int, slope_base: float = 0.0) -> None:
     """Prefill attention on the tcgen05 tensor cores: any number of new tokens per sequence, at consecutive
-    positions; ``status`` is an int32 word on the device that receives a code if a bounded wait runs out."""
+    positions; ``status`` is an int32 word on the device that receives a code if a bounded wait runs out.
+    ``slope_base`` as in ``attention``."""
     n = q.shape[0]
     assert q.shape == (n, n_heads * head_dim) and out.shape == q.shape and cu_seqlens.numel() >= n_seqs + 1
     assert q.is_contiguous() and out.is_contiguous() and k_pages.is_contiguous() and v_pages.is_contiguous()
@@ -468,7 +469,7 @@ def attention_prefill_tc(q, k_pages, v_pages, block_table, cu_seqlens, tok_pos, 
     assert status.dtype == torch.int32
     _call("attention_tc", "nncpu_attention_prefill_tc", _ptr(q), _ptr(k_pages), _ptr(v_pages), _i(k_pages.shape[0]),
           _ptr(block_table), _i(block_table.shape[1]), _ptr(cu_seqlens), _ptr(tok_pos), _ptr(out), _i(n), _i(n_seqs),
-          _i(n_heads), _i(n_kv), _i(head_dim), _f(scale), _i(window), _ptr(status), _stream())
+          _i(n_heads), _i(n_kv), _i(head_dim), _f(scale), _i(window), _f(slope_base), _ptr(status), _stream())
 
 
 def swiglu(gate_up, out) -> None:
@@ -512,6 +513,12 @@ def gla_step(proj, z, state, seq_slots, weight, eps: float, out, n_heads: int, d
     _call("recurrent", "nncpu_gla_step", _ptr(proj), _i(proj.shape[1]), _ptr(z), _ptr(state), _ptr(seq_slots),
           _ptr(weight), _i(_code(weight)), _f(eps), _ptr(out), _i(_code(out)), _i(n), _i(n_heads), _i(d), _i(e),
           _f(q_scale), _f(tau), _stream())
+
+
+def gla_scan_force_columns(cpl: int) -> None:
+    """For measurements and tests: the scan runs with 2 or 4 columns of the state per lane whatever the grid's size;
+    0: chosen by the grid (2, with twice the warps, where the blocks would not fill the GPU four times over)."""
+    library.load("recurrent").nncpu_gla_scan_force_columns(ctypes.c_int(int(cpl)))
 
 
 def gla_scan(proj, z, state, seq_slots, cu_seqlens, o, n_seqs: int, n_heads: int, d: int, e: int, q_scale: float,

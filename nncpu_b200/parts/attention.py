@@ -45,8 +45,8 @@ class Attention(Mixer):
         self.v_size = 0 if reads_other_cache else s.n_kv_heads * self.v_dim
         self.out_size = s.n_heads * self.v_dim
         # Value heads of their own size are known to the 32-bit kernel alone.  A distance bias or a query temperature
-        # keeps the step off the fused epilogues and off the tcgen05 prompt kernel (which know neither): the
-        # temperature is applied where q is made, the bias inside the mma.sync kernels for prompts and decode steps.
+        # keeps the step off the fused q/k/v epilogues (which know neither): the temperature is applied where q is
+        # made, the bias inside the attention kernels (tcgen05 for prompts, mma.sync for decode steps and short portions).
         self.plain_core = self.v_dim != s.head_dim
         self.unfused = self.plain_core or s.slope_base != 0.0 or s.q_temp_coef != 0.0
         self.q_temp = (s.q_temp_coef, s.q_temp_every) if s.q_temp_coef != 0.0 else None
@@ -204,12 +204,12 @@ class Attention(Mixer):
             ops.attention_decode_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos,
                                      attn, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, n_splits,
                                      s.slope_base)
-        elif not self.unfused and ctx.n_tokens >= 32 * ctx.n_seqs and ops.attention_prefill_tc_supported(
+        elif ctx.n_tokens >= 32 * ctx.n_seqs and ops.attention_prefill_tc_supported(
                 s.n_heads, s.n_kv_heads, s.head_dim, q, cache.k_pages, attn):
             # prompts: 128-row tiles on the tcgen05 tensor cores
             ops.attention_prefill_tc(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.cu_seqlens, ctx.tok_pos,
                                      attn, self.rt.workspace.status, ctx.n_seqs, s.n_heads, s.n_kv_heads, s.head_dim,
-                                     s.scale, s.window)
+                                     s.scale, s.window, s.slope_base)
         else:
             # a few new tokens per sequence: 64-row tiles
             ops.attention_prefill_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.cu_seqlens, ctx.tok_pos,

@@ -143,8 +143,16 @@ def test_embedding_with_learned_positions():
     check(out, want, 1e-6, "embedding plus position")
 
 
+@pytest.fixture(params=[2, 4])
+def scan_columns(request):
+    """Both arrangements of the scan kernel, whatever the grid's size would choose."""
+    ops.gla_scan_force_columns(request.param)
+    yield request.param
+    ops.gla_scan_force_columns(0)
+
+
 @pytest.mark.parametrize("H,d,e", [(3, 20, 48), (1, 64, 128), (2, 130, 33), (4, 128, 64)])
-def test_gla_recurrence_alone_in_portions_and_batches(H, d, e):
+def test_gla_recurrence_alone_in_portions_and_batches(H, d, e, scan_columns):
     """Three sequences of unequal lengths in one step against each alone, then the same tokens cut into portions
     (2, 1, 5, ... tokens) with the state carried in the state area, against the plain recurrence."""
     g = torch.Generator().manual_seed(d)
@@ -306,6 +314,13 @@ def test_biased_attention_on_the_tensor_core_kernels(nh, nkv, hd, window):
         q[b].double().numpy(), ks[b].double().numpy(), vs[b].double().numpy(), range(lens[b] - new[b], lens[b]), 0.2,
         window or None, slopes)) for b in range(3)]).view(n, -1)
     check(out, want, 2e-2, "prompt kernel with distance bias")
+    if ops.attention_prefill_tc_supported(nh, nkv, hd):
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        out_tc = torch.empty_like(out)
+        ops.attention_prefill_tc(torch.cat(q).view(n, -1).to(DEV), kp, vp, table, cu, tok_pos, out_tc, status, 3, nh, nkv, hd,
+                                 0.2, window, 8.0)
+        assert int(status.item()) == 0
+        check(out_tc, want, 2e-2, "tcgen05 prompt kernel with distance bias")
     last = torch.stack([q[b][-1] for b in range(3)]).view(3, -1).to(DEV)
     seq = torch.arange(3, dtype=torch.int32, device=DEV)
     pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)
@@ -535,3 +550,31 @@ def test_model_folder_as_other_tools_write_it(tmp_path):
     got = engine.step([engine.alloc_slot()], [t], [list(range(20))])
     check(got, plain_logits(folder, t), TOL["float32"], "rank from the file")
     assert model.info()["architecture"] == "Romepel"
+
+
+def test_command_line_random_weights_info_and_generation(tmp_path, capfd):
+    """The command line's modes on this design: a folder with random weights from a configuration file, its --info,
+    the greedy token harness against the plain model, and a sampled continuation (device-side sampling chain)."""
+    from nncpu_b200.cli import main
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps(CONFIGS["R"]))
+    assert main(["--random-weights", str(cfg), "5", str(tmp_path / "m"), "--fp32"]) == 0
+    capfd.readouterr()
+    assert main(["--info", str(tmp_path / "m")]) == 0
+    info = json.loads(capfd.readouterr().out)
+    assert info["config"]["architecture"] == "Romepel" and info["parameters"] > 0
+    prompt = toks(CONFIGS["R"], 40, 3)
+    assert main(["--gen", str(tmp_path / "m"), " ".join(map(str, prompt)), "8", "--fp32"]) == 0
+    got = [int(t) for t in capfd.readouterr().out.splitlines()[0].split()]
+    pcfg, w = P.load(tmp_path / "m")
+    seq = P.Sequence()
+    logits = P.forward(pcfg, w, prompt, seq)
+    want = []
+    for _ in range(8):
+        want.append(int(np.argmax(logits[-1])))
+        logits = P.forward(pcfg, w, [want[-1]], seq)
+    assert got == want
+    assert main(["-m", str(tmp_path / "m"), "--tokens", " ".join(map(str, prompt)), "-n", "6", "--temp", "0.8", "--top-k", "20",
+                 "-s", "4", "-b", "3"]) == 0
+    out = capfd.readouterr().out.split()
+    assert len(out) >= 6 and all(0 <= int(t) < CONFIGS["R"]["vocab"] for t in out[:6])
