@@ -108,7 +108,18 @@ struct NormFusion {
     // consumer: X is such an input; the rows' scales are applied to this product's result
     const unsigned long long* bins_in;   // [rows, kBinWords]
     float eps;
+    // an activation on the product's result (after the bias, plain epilogue, no accumulation): 0 none, 1 xIELU with
+    // its two numbers ready-made, act_a = softplus(p) and act_b = 1/2 + softplus(q)
+    int act;
+    float act_a, act_b;
 };
+
+constexpr int kActNone = 0, kActXielu = 1;
+
+// xIELU: a z^2 + z / 2 above zero, b (exp(z) - 1 - z) + z / 2 below, with a = softplus(p), b = 1/2 + softplus(q).
+__device__ __forceinline__ float xielu_f(float z, float a, float b) {
+    return z > 0.0f ? fmaf(a * z, z, 0.5f * z) : fmaf(b, expm1f(z) - z, 0.5f * z);
+}
 
 // A non-negative float into its row's accumulator: value = mantissa * 2^(E - 150) with E = 32 * bin + shift.
 __device__ __forceinline__ void bins_add(unsigned long long* bins, float v) {

@@ -141,6 +141,10 @@ __device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, 
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] += ld_f(p.bias, b0 + j, p.bias_dt);
             }
+            if (p.nf.act == kActXielu) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = xielu_f(v[j], p.nf.act_a, p.nf.act_b);
+            }
             if (p.out_dt == DT_F32) {
                 float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o);
                 if (p.accumulate) {
@@ -184,6 +188,7 @@ __device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, 
             if (col >= p.rows_b) break;
             float x = v[j];
             if (p.bias) x += ld_f(p.bias, col, p.bias_dt);
+            if (p.nf.act == kActXielu) x = xielu_f(x, p.nf.act_a, p.nf.act_b);
             if (p.accumulate) x += ld_f(p.out, o + j, p.out_dt);
             st_f(p.out, o + j, p.out_dt, x);
         }
@@ -201,7 +206,9 @@ __device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, 
         for (int j = 0; j < 16; ++j) {
             const int tok = b0 + j;
             if (tok >= p.rows_b || j >= ncols) break;
-            st_f(p.out, (size_t)tok * p.ldc + a_row, p.out_dt, (v[j] + b) + old[j]);
+            float x = v[j] + b;
+            if (p.nf.act == kActXielu) x = xielu_f(x, p.nf.act_a, p.nf.act_b);
+            st_f(p.out, (size_t)tok * p.ldc + a_row, p.out_dt, x + old[j]);
         }
     }
 }
@@ -917,7 +924,9 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int j = 0; j < 16; ++j) {
                     const int tok = n0 + c_begin + j;
                     const bool ok = j < n && tok < p.rows_b;        // the same for the whole warp
-                    const float y = (v[j] + b) + old[j];
+                    float x = v[j] + b;
+                    if (p.nf.act == kActXielu) x = xielu_f(x, p.nf.act_a, p.nf.act_b);
+                    const float y = x + old[j];
                     if (ok && a_ok) st_f(p.out, (size_t)tok * p.ldc + a_row, p.out_dt, y);
                     if (p.nf.xg_out != nullptr && ok) {
                         // the norm after this product rides on it: out * gamma for its consumer, and the token's sum
@@ -1671,7 +1680,7 @@ extern "C" int nncpu_linear_tc_norm_roles(int M, int N, int K) {
 extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt, int M,
                                int N, int K, int lda, int ldc, int accumulate, int epilogue, int plan, void* xg_out,
                                const void* gamma, int gamma_dt, void* bins_out, void* bins_clear, const void* bins_in,
-                               float eps, float* scratch, int* status, void* stream_) {
+                               float eps, int act, float act_a, float act_b, float* scratch, int* status, void* stream_) {
     const int streamk_mode = (plan & kPlanNeverEven) ? 0 : (plan & kPlanEvenFrom17) ? 2 : 1;
     const int pair_mode = (plan & kPlanNoPairs) ? 0 : 1;
     cudaStream_t stream = (cudaStream_t)stream_;
@@ -1714,6 +1723,9 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
         p.nf.bins_in = (const unsigned long long*)bins_in;
         p.nf.eps = eps;
     }
+    NN_CHECK(act == kActNone || (act == kActXielu && epilogue == kPlain && !accumulate && xg_out == nullptr),
+             "gemm: an activation (%d) goes with the plain epilogue, without accumulation or a norm after it", act);
+    p.nf.act = act; p.nf.act_a = act_a; p.nf.act_b = act_b;
     CUtensorMap ma, mb;
     int bn;
     if (M <= 256) {

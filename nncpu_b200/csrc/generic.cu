@@ -681,8 +681,7 @@ __global__ void xielu_kernel(const void* __restrict__ x, int in_dt, const void* 
     const float a_pos = softplus_f(ld_f(params, 0, p_dt));
     const float a_neg = 0.5f + softplus_f(ld_f(params, 1, p_dt));
     const float z = ld_f(x, (size_t)idx, in_dt);
-    const float y = z > 0.0f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);
-    st_f(out, (size_t)idx, out_dt, y);
+    st_f(out, (size_t)idx, out_dt, xielu_f(z, a_pos, a_neg));
 }
 
 // The prompt's case: float32 in, bfloat16 out, four elements a thread (16 bytes in, 8 out).
@@ -698,7 +697,7 @@ xielu_f32_bf16_kernel(const float4* __restrict__ x, const void* __restrict__ par
     float y[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e)
-        y[e] = z[e] > 0.0f ? fmaf(a_pos * z[e], z[e], 0.5f * z[e]) : fmaf(a_neg, expm1f(z[e]) - z[e], 0.5f * z[e]);
+        y[e] = xielu_f(z[e], a_pos, a_neg);
     __nv_bfloat162 h[2] = {__floats2bfloat162_rn(y[0], y[1]), __floats2bfloat162_rn(y[2], y[3])};
     out[idx] = *reinterpret_cast<uint2*>(h);
 }

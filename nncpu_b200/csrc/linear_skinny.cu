@@ -244,6 +244,7 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
                 for (int w = 0; w < kW; ++w) v += part[w][j][tok];
                 if (nf.bins_in != nullptr) v *= row_scale[tok];
                 if (bias) v += ld_f(bias, row, bias_dt);
+                if (nf.act == kActXielu) v = xielu_f(v, nf.act_a, nf.act_b);
                 if (accumulate) v += before[e];
                 st_f(out, (size_t)tok * ldc + row, out_dt, v);
             }
@@ -337,7 +338,8 @@ extern "C" int nncpu_linear_skinny_norm_words() { return 16 * kBinWords; }
 extern "C" int nncpu_linear_skinny(const void* X, const void* W, const void* bias, int bias_dt, void* C, int c_dt,
                                    int M, int N, int K, int lda, int ldc, int accumulate, int epilogue, void* xg_out,
                                    const void* gamma, int gamma_dt, void* bins_out, void* bins_clear,
-                                   const void* bins_in, float eps, int after_skinny, void* stream_) {
+                                   const void* bins_in, float eps, int act, float act_a, float act_b, int after_skinny,
+                                   void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     NN_CHECK(nncpu_linear_skinny_supported(M, N, K, lda),
              "linear (few tokens): M %d, N %d, K %d, lda %d: at most 16 tokens, K and lda multiples of 8", M, N, K, lda);
@@ -346,6 +348,9 @@ extern "C" int nncpu_linear_skinny(const void* X, const void* W, const void* bia
     const int n_out = epilogue == kSwiglu ? N / 2 : N;
     NN_CHECK(ldc >= n_out, "linear (few tokens): ldc %d is below the %d output features", ldc, n_out);
     NormFusion nf{};
+    NN_CHECK(act == kActNone || (act == kActXielu && epilogue == kPlain && !accumulate && xg_out == nullptr),
+             "linear (few tokens): an activation (%d) goes with the plain epilogue, without accumulation or a norm after it", act);
+    nf.act = act; nf.act_a = act_a; nf.act_b = act_b;
     if (xg_out != nullptr) {
         NN_CHECK(epilogue == kPlain && gamma != nullptr && bins_out != nullptr && ((uintptr_t)bins_out % 8) == 0 &&
                      ((uintptr_t)bins_clear % 8) == 0,

@@ -188,6 +188,38 @@ def rmsnorm(args) -> None:
     print(f"rmsnorm rows={rows} dim={dim}: {ms * 1e3:.1f} us, {rows * dim * 6 / ms / 1e6:.0f} GB/s")
 
 
+def gla(args) -> None:
+    """Gated linear attention's recurrence: the scan over `tokens` tokens of `batch` sequences (tokens > 1), or the
+    decode step's kernel (tokens == 1: recurrence, norm and gate in one launch)."""
+    b, t, h, d, e = args.batch, args.tokens, args.heads, args.key_dim, args.value_dim
+    n = b * t
+    ops.gla_scan_force_columns(args.columns)
+    proj = torch.randn(n, 2 * h * (d + e), device=DEV) * 0.1
+    state = torch.zeros(b + 1, h, d, e, device=DEV)
+    slots = torch.arange(b, dtype=torch.int32, device=DEV)
+    if t == 1:
+        z = torch.randn(n, h * d, device=DEV) + 3
+        w = torch.ones(e, device=DEV)
+        out = torch.empty(n, h * e, dtype=torch.bfloat16, device=DEV)
+        flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=DEV)      # the state of a step comes from memory
+
+        def call():
+            flush.zero_()
+            ops.gla_step(proj, z, state, slots, w, 1e-6, out, h, d, e, d ** -0.5, 16.0)
+        ms_all = _time([call], args.once)
+        ms_flush = _time([lambda: flush.zero_()], args.once)
+        ms = ms_all - ms_flush
+        print(f"gla step batch={b} heads={h} d={d} e={e}: {ms * 1e3:.1f} us, {8.0 * b * h * d * e / ms / 1e6:.0f} GB/s of state")
+        return
+    z = torch.sigmoid(torch.randn(n, h * d, device=DEV) + 3)
+    cu = torch.arange(0, n + 1, t, dtype=torch.int32, device=DEV)
+    o = torch.empty(n, h * e, device=DEV)
+    ms = _time([lambda: ops.gla_scan(proj, z, state, slots, cu, o, b, h, d, e, d ** -0.5, 16.0, decays_given=True)], args.once)
+    nbytes = 4.0 * (proj.numel() + z.numel() + o.numel())
+    print(f"gla scan batch={b} tokens={t} heads={h} d={d} e={e}: {ms * 1e3:.1f} us, {2.0 * n * h * d * e / ms / 1e9:.2f} T multiply-adds/s, "
+          f"{nbytes / ms / 1e6:.0f} GB/s of inputs and outputs")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--once", action="store_true", help="three plain launches, no timing (for a profiler)")
@@ -224,6 +256,12 @@ def main(argv=None) -> int:
     p = sub.add_parser("rmsnorm")
     p.add_argument("rows", type=int); p.add_argument("dim", type=int)
     p.set_defaults(fn=rmsnorm)
+    p = sub.add_parser("gla")
+    p.add_argument("batch", type=int); p.add_argument("tokens", type=int)
+    p.add_argument("--heads", type=int, default=8); p.add_argument("--key-dim", type=int, default=128)
+    p.add_argument("--value-dim", type=int, default=256)
+    p.add_argument("--columns", type=int, default=0, choices=[0, 2, 4], help="columns of the state a lane (0: by the grid's size)")
+    p.set_defaults(fn=gla)
     args = ap.parse_args(argv)
     if args.no_overlap:
         ops.launch_overlap(False)

@@ -193,6 +193,17 @@ PLANS = {"auto": 0, "even_from_17": 1, "never_even": 2, "no_pairs": 4, "narrow_u
 EPILOGUES = {"plain": 0, "swiglu": 1}
 
 
+def _activation(activation):
+    """``activation`` None, or ("xielu", a, b) with a = softplus(p) and b = 1/2 + softplus(q) ready-made: applied to
+    the product's result after the bias (plain epilogue, no accumulation)."""
+    if activation is None:
+        return _i(0), _f(0.0), _f(0.0)
+    kind, a, b = activation
+    if kind != "xielu":
+        raise InvalidArgument(f"a product cannot apply the activation {kind!r}")
+    return _i(1), _f(a), _f(b)
+
+
 @functools.lru_cache(maxsize=4096)
 def linear_tc_fuses_norms(m: int, n: int) -> bool:
     """Whether the tensor-core product of ``m`` tokens with ``n`` output features can carry the norms around it
@@ -209,7 +220,7 @@ def linear_tc_norm_roles(m: int, n: int, k: int) -> int:
 
 
 def linear_tc(x, w, bias, out, workspace: GemmWorkspace, accumulate: bool = False, epilogue: str = "plain",
-              plan: str = "auto", norm_out=None, norm_in=None) -> None:
+              plan: str = "auto", norm_out=None, norm_in=None, activation=None) -> None:
     """out (+)= x . w^T + bias on the tensor cores; x and w bfloat16.  With
     ``epilogue="swiglu"`` the rows of w hold gate and up rows interleaved in
     blocks of 8 and out [m, n/2] receives silu(gate) * up.  ``plan``: "auto",
@@ -236,7 +247,7 @@ def linear_tc(x, w, bias, out, workspace: GemmWorkspace, accumulate: bool = Fals
     _call("gemm_sm100", "nncpu_linear_tc", _ptr(x), _ptr(w), _ptr(bias), _i(_code(bias)), _ptr(out),
           _i(_code(out)), _i(m), _i(n), _i(k), _i(x.stride(0)), _i(out.shape[1]), _i(accumulate), _i(EPILOGUES[epilogue]),
           _i(PLANS[plan]), _ptr(xg), _ptr(gamma), _i(_code(gamma)), _ptr(bins_out), _ptr(bins_clear), _ptr(bins_in),
-          _f(eps), _ptr(workspace.scratch), _ptr(workspace.status), _stream())
+          _f(eps), *_activation(activation), _ptr(workspace.scratch), _ptr(workspace.status), _stream())
 
 
 def linear_tc_wait_probe(x, w, out, workspace: GemmWorkspace, limit_ms: int = 5) -> None:
@@ -284,7 +295,7 @@ CLUSTER_MAX_TOKENS = 64    # up to here a tensor-core product's weights are the 
 
 
 def linear_skinny(x, w, bias, out, accumulate: bool = False, epilogue: str = "plain", norm_out=None,
-                  norm_in=None) -> None:
+                  norm_in=None, activation=None) -> None:
     """The same product for at most 16 tokens: a stream over the weights that
     uses every SM, with no scratch memory.
 
@@ -314,7 +325,7 @@ def linear_skinny(x, w, bias, out, accumulate: bool = False, epilogue: str = "pl
     _call("linear_skinny", "nncpu_linear_skinny", _ptr(x), _ptr(w), _ptr(bias), _i(_code(bias)), _ptr(out),
           _i(_code(out)), _i(m), _i(n), _i(k), _i(k), _i(out.shape[1]), _i(accumulate), _i(EPILOGUES[epilogue]),
           _ptr(xg), _ptr(gamma), _i(_code(gamma)), _ptr(bins_out), _ptr(bins_clear), _ptr(bins_in), _f(eps),
-          _i(after_skinny), _stream())
+          *_activation(activation), _i(after_skinny), _stream())
 
 
 def linear_skinny_force_warps(warps: int) -> None:

@@ -67,9 +67,9 @@ class GatedMlp(FeedForward):
 
 @register_feed_forward("dense_mlp")
 class DenseMlp(FeedForward):
-    """down(xielu(up(x) + b_up)) + b_down.  The up product's result stays in float32 and the activation
-    (softplus of its two numbers included) is computed in 32-bit; its output is rounded to the run's element type
-    for the down product.  Tensors: ``<name>.up``, ``.up.b``, ``.down``, ``.down.b``, ``.act`` (p, q)."""
+    """down(xielu(up(x) + b_up)) + b_down.  The activation (softplus of its two numbers included) is computed in
+    32-bit on the up product's 32-bit result, in the product's epilogue where it runs on the tensor cores and in a
+    kernel of its own elsewhere; its output is rounded to the run's element type for the down product.  Tensors: ``<name>.up``, ``.up.b``, ``.down``, ``.down.b``, ``.act`` (p, q)."""
 
     def __init__(self, spec):
         if spec.activation != "xielu":
@@ -89,6 +89,12 @@ class DenseMlp(FeedForward):
         self.w_up, self.b_up = tensors[f"{s.name}.up"], tensors[f"{s.name}.up.b"]
         self.w_down, self.b_down = tensors[f"{s.name}.down"], tensors[f"{s.name}.down.b"]
         self.act = tensors[f"{s.name}.act"]
+        # On the tensor-core path the activation runs in the up product's epilogue, on its 32-bit accumulators; its
+        # two numbers enter as softplus(p) and 1/2 + softplus(q), worked out once here in 32-bit.
+        self.fused = rt.tensor_cores_take(rt.dtype, self.w_up, s.hidden_size) and not self.act.is_meta
+        if self.fused:
+            p, q = torch.nn.functional.softplus(self.act.detach().float().cpu()).tolist()
+            self.activation = ("xielu", p, 0.5 + q)
 
     def weight_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down))
@@ -96,11 +102,15 @@ class DenseMlp(FeedForward):
     def forward(self, ctx, x, residual):
         s, rt = self.spec, self.rt
         n = x.shape[0]
-        up = rt.empty(n, s.intermediate_size, dtype=torch.float32)
-        with rt.phase("ffn_up", self.w_up, n):
-            rt.linear(x, self.w_up, self.b_up, up)
         act = rt.empty(n, s.intermediate_size)
-        with rt.phase("ffn_act"):
-            ops.xielu(up, self.act, act)
+        if self.fused:
+            with rt.phase("ffn_up", self.w_up, n):
+                rt.linear(x, self.w_up, self.b_up, act, activation=self.activation)
+        else:
+            up = rt.empty(n, s.intermediate_size, dtype=torch.float32)
+            with rt.phase("ffn_up", self.w_up, n):
+                rt.linear(x, self.w_up, self.b_up, up)
+            with rt.phase("ffn_act"):
+                ops.xielu(up, self.act, act)
         with rt.phase("ffn_down", self.w_down, n):
             rt.linear(act, self.w_down, self.b_down, residual, accumulate=not getattr(ctx, "branch_is_fresh", False))

@@ -148,14 +148,17 @@ class Runtime:
     def tensor_cores_take(self, x_dtype, w, k: int) -> bool:
         return x_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ops.linear_tc_supported(1, w.shape[0], k)
 
-    def linear(self, x, w, bias, out, accumulate: bool = False, epilogue: str = "plain", then_norm=None) -> None:
+    def linear(self, x, w, bias, out, accumulate: bool = False, epilogue: str = "plain", then_norm=None,
+               activation=None) -> None:
         """out (+)= x . w^T + bias.  bfloat16 inputs whose sizes keep TMA's
         alignment rule go to the tensor cores; everything else, and every
         float32 product, runs in true 32-bit on CUDA cores.
 
         ``x`` may be a ``DeferredNorm`` (a norm's unfinished output): the few-token product and the product of
         whole prompts finish it, any other path makes the ordinary tensor first.  ``then_norm`` (a ``NormRequest``):
-        this product is the last write into ``out`` before that norm reads it; the same two products fulfil it."""
+        this product is the last write into ``out`` before that norm reads it; the same two products fulfil it.
+        ``activation`` (("xielu", a, b), see ``ops.linear_tc``): applied in the product's epilogue on its 32-bit
+        accumulators; only where ``tensor_cores_take`` says the product runs on the tensor cores."""
         deferred = x if isinstance(x, DeferredNorm) else None
         takes = self.tensor_cores_take(x.dtype, w, x.shape[1])
         few = takes and x.shape[0] <= ops.SKINNY_MAX_TOKENS
@@ -185,13 +188,14 @@ class Runtime:
             if few:
                 ops.linear_skinny(x, w, bias, out, accumulate, epilogue,
                                   norm_out and (norm_out[0], norm_out[1], norm_out[2].view(-1), norm_out[3].view(-1)),
-                                  norm_in and (norm_in[0].view(-1), norm_in[1]))
+                                  norm_in and (norm_in[0].view(-1), norm_in[1]), activation=activation)
             else:
-                ops.linear_tc(x, w, bias, out, self.workspace, accumulate, epilogue, norm_out=norm_out, norm_in=norm_in)
+                ops.linear_tc(x, w, bias, out, self.workspace, accumulate, epilogue, norm_out=norm_out, norm_in=norm_in,
+                              activation=activation)
             if norm_out is not None:
                 then_norm.result = made
         else:
-            assert epilogue == "plain", "the fused epilogue exists on the tensor-core path only"
+            assert epilogue == "plain" and activation is None, "fused epilogues exist on the tensor-core path only"
             ops.linear_simt(x, w, bias, out, accumulate)
 
     def fuses_norms(self, n_tokens: int, n_out: int) -> bool:

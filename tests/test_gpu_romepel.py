@@ -131,6 +131,31 @@ def test_xielu_both_branches_and_soft_cap():
     check(x, want, 1e-6, "soft cap")
 
 
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 40, 64, 100, 256, 300, 600, 1100])
+def test_xielu_in_the_epilogue_of_the_tensor_core_products(m):
+    """Every product kernel (few tokens, cluster, stream-K, persistent, pairs of SMs) with the activation on its
+    accumulators, against the product in float32 followed by the activation's own kernel."""
+    from nncpu_b200.parts import Runtime
+    rt = Runtime(DEV, torch.bfloat16)
+    g = torch.Generator().manual_seed(m)
+    k, n = 192, 328
+    x = (torch.randn(m, k, generator=g) * 2).bfloat16().to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.2).bfloat16().to(DEV)
+    bias = torch.randn(n, generator=g).bfloat16().to(DEV)
+    params = torch.tensor([0.4, -0.3])
+    a, b = torch.nn.functional.softplus(params).tolist()
+    plain = torch.empty(m, n, device=DEV)
+    rt.linear(x, w, bias, plain)
+    want = torch.empty(m, n, device=DEV)
+    ops.xielu(plain, params.to(DEV), want)
+    for out_dt in (torch.bfloat16, torch.float32):
+        got = torch.empty(m, n, dtype=out_dt, device=DEV)
+        rt.linear(x, w, bias, got, activation=("xielu", a, 0.5 + b))
+        torch.cuda.synchronize()
+        rt.check_status()
+        check(got, want, 1e-5 if out_dt == torch.float32 else 8e-3, f"{m} tokens")
+
+
 def test_embedding_with_learned_positions():
     g = torch.Generator().manual_seed(3)
     table, pos = torch.randn(50, 24, generator=g), torch.randn(30, 24, generator=g)
@@ -552,20 +577,24 @@ def test_model_folder_as_other_tools_write_it(tmp_path):
     assert model.info()["architecture"] == "Romepel"
 
 
-def test_command_line_random_weights_info_and_generation(tmp_path, capfd):
+def test_command_line_random_weights_info_and_generation(tmp_path):
     """The command line's modes on this design: a folder with random weights from a configuration file, its --info,
     the greedy token harness against the plain model, and a sampled continuation (device-side sampling chain)."""
-    from nncpu_b200.cli import main
+    import io
+    from nncpu_b200.cli import parse_options, run_gen, run_generate, run_info, run_random_weights
+
+    def run(fn, argv):
+        out = io.StringIO()
+        assert fn(parse_options(argv), out) == 0
+        return out.getvalue()
+
     cfg = tmp_path / "cfg.json"
     cfg.write_text(json.dumps(CONFIGS["R"]))
-    assert main(["--random-weights", str(cfg), "5", str(tmp_path / "m"), "--fp32"]) == 0
-    capfd.readouterr()
-    assert main(["--info", str(tmp_path / "m")]) == 0
-    info = json.loads(capfd.readouterr().out)
+    run(run_random_weights, ["--random-weights", str(cfg), "5", str(tmp_path / "m"), "--fp32"])
+    info = json.loads(run(run_info, ["--info", str(tmp_path / "m")]))
     assert info["config"]["architecture"] == "Romepel" and info["parameters"] > 0
     prompt = toks(CONFIGS["R"], 40, 3)
-    assert main(["--gen", str(tmp_path / "m"), " ".join(map(str, prompt)), "8", "--fp32"]) == 0
-    got = [int(t) for t in capfd.readouterr().out.splitlines()[0].split()]
+    got = [int(t) for t in run(run_gen, ["--gen", str(tmp_path / "m"), " ".join(map(str, prompt)), "8", "--fp32"]).splitlines()[0].split()]
     pcfg, w = P.load(tmp_path / "m")
     seq = P.Sequence()
     logits = P.forward(pcfg, w, prompt, seq)
@@ -574,7 +603,6 @@ def test_command_line_random_weights_info_and_generation(tmp_path, capfd):
         want.append(int(np.argmax(logits[-1])))
         logits = P.forward(pcfg, w, [want[-1]], seq)
     assert got == want
-    assert main(["-m", str(tmp_path / "m"), "--tokens", " ".join(map(str, prompt)), "-n", "6", "--temp", "0.8", "--top-k", "20",
-                 "-s", "4", "-b", "3"]) == 0
-    out = capfd.readouterr().out.split()
+    out = run(run_generate, ["-m", str(tmp_path / "m"), "--tokens", " ".join(map(str, prompt)), "-n", "6", "--temp", "0.8",
+                             "--top-k", "20", "-s", "4", "-b", "3"]).split()
     assert len(out) >= 6 and all(0 <= int(t) < CONFIGS["R"]["vocab"] for t in out[:6])
