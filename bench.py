@@ -247,9 +247,9 @@ def romepel_configs(z: dict):
     from nncpu_b200.config import config_from_dict
     att = {"type": "attention", "mlp": {"kind": "dense", "ff": z["inter"] * 3 // 2},
            "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
-                     "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}, "q_temp": {"coef": 0.3, "every": 128}}}
+                     "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}, "q_temp": {"coef": 0.25, "every": 256}}}
     gla = {"type": "gla", "mlp": {"kind": "dense", "ff": z["inter"] * 3 // 2},
-           "mixer": {"heads": z["gla_heads"], "dim": z["gla_dim"], "vdim": z["gla_vdim"], "tau": 16.0, "rank": z["rank"]}}
+           "mixer": {"heads": z["gla_heads"], "dim": z["gla_dim"], "vdim": z["gla_vdim"], "tau": 8.0, "rank": z["rank"]}}
     layers = [gla if i % 3 == 0 else att for i in range(z["layers"])]
     rom = config_from_dict({"architecture": "Romepel", "vocab": z["vocab"], "width": z["width"], "max_positions": CONTEXT,
                             "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": layers})

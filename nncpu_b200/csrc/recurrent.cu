@@ -57,7 +57,7 @@ gla_scan_kernel(const float* __restrict__ proj, int row, const float* __restrict
                 const int* __restrict__ seq_slots, const int* __restrict__ cu_seqlens, float* __restrict__ o, int H,
                 int d, int e, float q_scale, float inv_tau, int decays_given) {
     constexpr int DR = DMAX / 32;                             // rows of its columns that a lane keeps
-    constexpr int TB = DMAX <= 128 ? kScanGroup : kScanGroup / 2;   // tokens a group (shared memory: 2 TB DMAX 16 bytes)
+    constexpr int TB = DMAX <= 128 ? kScanGroup : DMAX <= 256 ? kScanGroup / 2 : kScanGroup / 4;   // tokens a group (shared memory: 2 TB DMAX 16 bytes)
     constexpr int kScanThreads = 32 * kScanCols / CPL;
     constexpr int PER = TB * DMAX / kScanThreads;             // (token, key channel) pairs a thread stages
     constexpr int N = CPL * TB;                               // partial sums a lane carries through a group
@@ -176,7 +176,7 @@ extern "C" int nncpu_gla_scan(const float* proj, int row, const float* z, float*
                               const int* cu_seqlens, float* o, int n_seqs, int H, int d, int e, float q_scale,
                               float tau, int decays_given, void* stream) {
     NN_CHECK(n_seqs >= 0 && H > 0 && d > 0 && e > 0, "gla_scan: %d sequences, %d heads of %d x %d", n_seqs, H, d, e);
-    NN_CHECK(d <= 256, "gla_scan: %d key channels a head (at most 256)", d);
+    NN_CHECK(d <= 512, "gla_scan: %d key channels a head (at most 512)", d);
     NN_CHECK(row >= 2 * H * d + 2 * H * e, "gla_scan: rows of %d floats for %d heads of %d x %d", row, H, d, e);
     NN_CHECK(tau > 0.0f, "gla_scan: tau %g", tau);
     NN_CHECK(H <= 65535 && (e + kScanCols - 1) / kScanCols <= 65535, "gla_scan: grid");
@@ -203,7 +203,8 @@ extern "C" int nncpu_gla_scan(const float* proj, int row, const float* z, float*
     if (d <= 32) NN_SCAN(32);
     else if (d <= 64) NN_SCAN(64);
     else if (d <= 128) NN_SCAN(128);
-    else NN_SCAN(256);
+    else if (d <= 256) NN_SCAN(256);
+    else NN_SCAN(512);
 #undef NN_SCAN
     NN_LAUNCH_OK("gla_scan");
     return 0;

@@ -26,7 +26,7 @@ from ..kernels import ops
 from ..weights.params import ParamSpec
 from .base import Mixer, register_mixer
 
-MAX_KEY_DIM = 256      # a lane of the scan kernel keeps one column of a head's state in registers
+MAX_KEY_DIM = 512      # a lane of the scan kernel keeps one column of a head's state in registers
 
 
 @register_mixer("gla")
