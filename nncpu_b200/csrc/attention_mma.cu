@@ -338,13 +338,16 @@ struct FusedQK {
     __nv_bfloat16* k_pages;   // the cache, writable; null: the keys and values are another entry's, nothing is appended
     __nv_bfloat16* v_pages;
     float slope_base;         // not of the projections: b != 0 gives head h the distance bias 2^(-b (h + 1) / n_heads) * (pos - key)
+    float temp_coef;          // c != 0: the query at position p is multiplied by 1 + c ln(floor((p + 1) / temp_every) + 1)
+    int temp_every;
 };
 
 // One head's HD float32 values through norm (if gamma) and rotation (if cs) to bfloat16; a warp's job.  A lane holds
 // HD / 32 neighbouring lanes of the head, so a rotation pair (i, i + HD / 2) sits in the lanes l and l ^ 16.
 template <int HD>
 __device__ __forceinline__ void finish_head(const float* __restrict__ src, const void* __restrict__ gamma, int g_dt, float eps,
-                                            const float2* __restrict__ cs_row, __nv_bfloat16* __restrict__ dst, int lane) {
+                                            const float2* __restrict__ cs_row, __nv_bfloat16* __restrict__ dst, int lane,
+                                            float times = 1.0f) {
     constexpr int EPL = HD / 32;
     float x[EPL];
     if (EPL == 4) {
@@ -372,6 +375,10 @@ __device__ __forceinline__ void finish_head(const float* __restrict__ src, const
             const float2 c = cs_row[i0 + e];
             x[e] = lane < 16 ? c.x * x[e] - c.y * other : c.y * other + c.x * x[e];
         }
+    }
+    if (times != 1.0f) {        // a query temperature
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) x[e] *= times;
     }
     if (EPL == 4) {
         __nv_bfloat162 o[2] = {__floats2bfloat162_rn(x[0], x[1]), __floats2bfloat162_rn(x[2 % EPL], x[3 % EPL])};
@@ -440,8 +447,9 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
     if constexpr (kFused) {
         const float* row = f.qkv + (size_t)t * f.per_tok * HD;
         const float2* cs_row = f.cs ? f.cs + (size_t)t * (HD / 2) : nullptr;
+        const float temp = f.temp_coef != 0.0f ? 1.0f + f.temp_coef * logf((float)((pos + 1) / f.temp_every) + 1.0f) : 1.0f;
         for (int g = warp; g < G; g += 4)
-            finish_head<HD>(row + (size_t)(kvh * G + g) * HD, f.q_gamma, f.g_dt, f.eps, cs_row, q_s + g * HD, lane);
+            finish_head<HD>(row + (size_t)(kvh * G + g) * HD, f.q_gamma, f.g_dt, f.eps, cs_row, q_s + g * HD, lane, temp);
         if (owner) {
             if (warp == 0)
                 finish_head<HD>(row + (size_t)(n_heads + kvh) * HD, f.k_gamma, f.g_dt, f.eps, cs_row, kv_s, lane);
@@ -683,7 +691,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
                                     : (G <= 8 ? (Kernel)decode_kernel<HD, 1, false, true> : (Kernel)decode_kernel<HD, 2, false, true>);
     const Kernel kernel = fused ? from_qkv : plain;
     FusedQK f = fused ? *fused : FusedQK{};
-    f.slope_base = slope_base;
+    if (!fused) f.slope_base = slope_base;
     const size_t stages = (size_t)kDecodeStages * 2 * kPage * HD * 2;
     const size_t merge = (size_t)5 * G * (HD + 2) * sizeof(float);
     const size_t smem = stages > merge ? stages : merge;
@@ -788,7 +796,8 @@ extern "C" int nncpu_attention_decode_mma_from_qkv(const float* qkv, const void*
                                                    int append, const int* block_table, int bt_stride,
                                                    const int* tok_seq, const int* tok_pos, void* out, float* scratch,
                                                    long scratch_floats, int n_tok, int n_heads, int n_kv, int hd,
-                                                   float scale, int window, int n_splits, void* stream) {
+                                                   float scale, int window, int n_splits, float slope_base,
+                                                   float temp_coef, int temp_every, void* stream) {
     NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
              "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
              "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
@@ -812,6 +821,10 @@ extern "C" int nncpu_attention_decode_mma_from_qkv(const float* qkv, const void*
     f.cs = (const float2*)cos_sin;
     f.k_pages = append ? (__nv_bfloat16*)k_pages : nullptr;
     f.v_pages = append ? (__nv_bfloat16*)v_pages : nullptr;
+    NN_CHECK(temp_coef == 0.0f || temp_every > 0, "attention decode: a query temperature every %d positions", temp_every);
+    f.slope_base = slope_base;
+    f.temp_coef = temp_coef;
+    f.temp_every = temp_every;
     if (hd == 64)
         return launch_decode<64>(nullptr, k_pages, v_pages, block_table, bt_stride, tok_seq, tok_pos, out, scratch, n_tok,
                                  n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream, &f);

@@ -45,8 +45,9 @@ class Attention(Mixer):
         self.v_size = 0 if reads_other_cache else s.n_kv_heads * self.v_dim
         self.out_size = s.n_heads * self.v_dim
         # Value heads of their own size are known to the 32-bit kernel alone.  A distance bias or a query temperature
-        # keeps the step off the fused q/k/v epilogues (which know neither): the temperature is applied where q is
-        # made, the bias inside the attention kernels (tcgen05 for prompts, mma.sync for decode steps and short portions).
+        # keeps a prompt step off the fused q/k/v epilogue of the projection (which knows neither): the temperature is
+        # applied where q is made (in a decode step: inside the attention kernel that starts from the projections),
+        # the bias inside the attention kernels (tcgen05 for prompts, mma.sync for decode steps and short portions).
         self.plain_core = self.v_dim != s.head_dim
         self.unfused = self.plain_core or s.slope_base != 0.0 or s.q_temp_coef != 0.0
         self.q_temp = (s.q_temp_coef, s.q_temp_every) if s.q_temp_coef != 0.0 else None
@@ -139,7 +140,7 @@ class Attention(Mixer):
                     ops.attention_decode_mma_from_qkv(qkv, self.q_gamma, self.k_gamma, eps, cos_sin, cache.k_pages,
                                                       cache.v_pages, not self.shared_kv, cache.block_table, ctx.tok_seq,
                                                       ctx.tok_pos, attn, scratch, s.n_heads, s.n_kv_heads, s.head_dim,
-                                                      s.scale, s.window, n_splits)
+                                                      s.scale, s.window, n_splits, s.slope_base, self.q_temp)
             else:
                 q = rt.empty(n, self.q_size)
                 with rt.phase("attn_rope"):
@@ -167,7 +168,7 @@ class Attention(Mixer):
         """Whether this step's attention can start from the float32 projections: a decode step on the tensor-core
         kernel, every lane of a head rotated (or none), norm weights of one type."""
         s = self.spec
-        return (not self.unfused and ctx.is_decode and self.rt.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
+        return (not self.plain_core and ctx.is_decode and self.rt.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
                 and ops.attention_mma_supported(s.n_heads, s.n_kv_heads, s.head_dim)
                 and (self.position is None or self.position.half * 2 == s.head_dim)
                 and (self.q_gamma is None or self.k_gamma is None or self.q_gamma.dtype == self.k_gamma.dtype))
