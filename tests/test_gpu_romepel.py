@@ -329,7 +329,8 @@ def test_biased_attention_alone(dtype, nh, nkv, hd, vd, window):
     check(out, want, 2e-5 if dtype == "float32" else 2e-2, "attention with distance bias")
 
 
-@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 64, 100), (2, 1, 128, 64), (8, 2, 64, 56), (16, 1, 64, 0), (12, 4, 128, 200)])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 64, 100), (2, 1, 128, 64), (8, 2, 64, 56), (16, 1, 64, 0), (12, 4, 128, 200),
+                                              (6, 2, 64, 30), (3, 1, 128, 0), (5, 5, 64, 70), (1, 1, 64, 3)])
 def test_biased_attention_on_the_tensor_core_kernels(nh, nkv, hd, window):
     """The bfloat16 kernels for prompts and for decode steps with the distance bias: three sequences (a portion of
     9 tokens, a whole prompt of 67, a portion of 130 that crosses two pages), then one token each, with the keys in
