@@ -12,6 +12,10 @@ steps; by default K extends the prompts to the full context (2,039 steps after
 with host token ids in and out.  The line also carries a prefill measurement (one
 2,048-token prompt), the decode step's memory roofline, decode at batch 1 and
 64, and the SM clocks sampled during the timed region.
+
+``--workload NAME`` runs another measurement instead and prints its own JSON: ``14b-unequal``, ``32b`` and
+``long-context`` (larger Qwen3 sizes end to end), and ``romepel`` (the Romepel design at two widths beside Qwen3 layers
+of equal size: a 2 048-token prompt, decode at batch 8, and every phase's time and roofline fraction).
 """
 from __future__ import annotations
 
