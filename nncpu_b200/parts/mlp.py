@@ -6,6 +6,8 @@ Dense: down(act(up(x) + b_up)) + b_down with act = xIELU, an activation with two
 """
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..errors import UnsupportedModel
@@ -93,7 +95,7 @@ class DenseMlp(FeedForward):
         # two numbers enter as softplus(p) and 1/2 + softplus(q), worked out once here in 32-bit.
         self.fused = rt.tensor_cores_take(rt.dtype, self.w_up, s.hidden_size) and not self.act.is_meta
         if self.fused:
-            p, q = torch.nn.functional.softplus(self.act.detach().float().cpu()).tolist()
+            p, q = (math.log1p(math.exp(-abs(v))) + max(v, 0.0) for v in self.act.detach().float().tolist())   # softplus
             self.activation = ("xielu", p, 0.5 + q)
 
     def weight_bytes(self):
