@@ -251,7 +251,8 @@ extern "C" int nncpu_gla_output(const float* o, const float* proj, int row, int 
 // columns, so a step reads and writes the state at full width and nothing of it stays in registers.  The decays, k
 // and q of the token are shared through shared memory; the head's sum of squares is a block sum.  A negative slot
 // (padding) gives zeros and touches no state.  Threads: e rounded up to a warp (e <= 1024).
-__global__ void __launch_bounds__(1024)
+template <int kThreads, int kInFlight>
+__global__ void __launch_bounds__(kThreads)
 gla_step_kernel(const float* __restrict__ proj, int row, const float* __restrict__ z, float* __restrict__ state,
                 const int* __restrict__ seq_slots, const void* __restrict__ w, int w_dt, float eps,
                 void* __restrict__ out, int out_dt, int H, int d, int e, float q_scale, float inv_tau) {
@@ -274,12 +275,14 @@ gla_step_kernel(const float* __restrict__ proj, int row, const float* __restrict
         const float v = p[2 * (size_t)H * d + (size_t)h * e + j];
         float* col = state + (((size_t)slot * H + h) * d) * e + j;
         int i = 0;
-        for (; i + 8 <= d; i += 8) {         // eight rows in flight (32 were slower at every batch size measured)
-            float s[8];
+        // kInFlight rows in flight: a step of few sequences is bound by the loads' latency, and a block of up to 256
+        // threads has the registers for 32 of them (a block of 1 024 threads has 64 registers a thread: 8)
+        for (; i + kInFlight <= d; i += kInFlight) {
+            float s[kInFlight];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) s[u] = col[(size_t)(i + u) * e];
+            for (int u = 0; u < kInFlight; ++u) s[u] = col[(size_t)(i + u) * e];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < kInFlight; ++u) {
                 const float4 c = akq[i + u];
                 s[u] = fmaf(c.x, s[u], c.y * v);
                 acc = fmaf(s[u], c.z, acc);
@@ -310,8 +313,22 @@ extern "C" int nncpu_gla_step(const float* proj, int row, const float* z, float*
     NN_CHECK(row >= 2 * H * d + 2 * H * e && tau > 0.0f, "gla_step: rows of %d floats, tau %g", row, tau);
     if (n_tok == 0) return 0;
     const int threads = (e + 31) / 32 * 32;
-    gla_step_kernel<<<dim3(n_tok, H), threads, (size_t)d * sizeof(float4), (cudaStream_t)stream>>>(
-        proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau);
+    int sms = 148;
+    {
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    // few blocks: each thread keeps 32 loads in flight (one block an SM); many blocks: 8, and the SM's other blocks
+    // fill the waits (batch 8 of 8 heads 20 -> 11 us with 32; batch 64 of 16 heads 57 us with 8, 78 with 32)
+    if (threads <= 256 && (long)n_tok * H <= 2L * sms)
+        gla_step_kernel<256, 32><<<dim3(n_tok, H), threads, (size_t)d * sizeof(float4), (cudaStream_t)stream>>>(
+            proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau);
+    else if (threads <= 256)
+        gla_step_kernel<256, 8><<<dim3(n_tok, H), threads, (size_t)d * sizeof(float4), (cudaStream_t)stream>>>(
+            proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau);
+    else
+        gla_step_kernel<1024, 8><<<dim3(n_tok, H), threads, (size_t)d * sizeof(float4), (cudaStream_t)stream>>>(
+            proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau);
     NN_LAUNCH_OK("gla_step");
     return 0;
 }
