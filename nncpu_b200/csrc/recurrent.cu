@@ -20,6 +20,19 @@
 
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
+// Two 32-bit multiply-adds in one instruction (sm_100 has them for pairs of floats in a 64-bit register): each half is
+// an ordinary fused multiply-add with round-to-nearest, so results are those of two fmaf calls.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    unsigned long long ra, rb, rc, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+
 // The decays of a prompt's tokens, made once for all the blocks that read them: z <- sigmoid(z)^(1/tau) in place.
 __global__ void gla_decay_kernel(float* __restrict__ z, long n, float inv_tau) {
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -74,12 +87,15 @@ gla_scan_kernel(const float* __restrict__ proj, int row, const float* __restrict
         return;
     }
     float* s_head = state + ((size_t)slot * H + h) * (size_t)d * e;
-    float S[DR][CPL];
+    float2 S[DR][CPL / 2];          // pairs of neighbouring columns: the recurrence runs on two at a time
 #pragma unroll
     for (int ii = 0; ii < DR; ++ii) {
         const int i = ii * 32 + lane;
 #pragma unroll
-        for (int c = 0; c < CPL; ++c) S[ii][c] = (i < d && j0 + c < e) ? s_head[(size_t)i * e + j0 + c] : 0.0f;
+        for (int c = 0; c < CPL; c += 2) {
+            S[ii][c / 2].x = (i < d && j0 + c < e) ? s_head[(size_t)i * e + j0 + c] : 0.0f;
+            S[ii][c / 2].y = (i < d && j0 + c + 1 < e) ? s_head[(size_t)i * e + j0 + c + 1] : 0.0f;
+        }
     }
     const size_t q_at = (size_t)h * d, k_at = (size_t)H * d + (size_t)h * d, v_at = 2 * (size_t)H * d + (size_t)h * e;
     // The tokens come in groups of TB: a group's q, k, v and decay logits are fetched into registers while the group
@@ -122,23 +138,34 @@ gla_scan_kernel(const float* __restrict__ proj, int row, const float* __restrict
         float x[N];
 #pragma unroll
         for (int tt = 0; tt < TB; ++tt) {
+            float2 xs[CPL / 2];
 #pragma unroll
-            for (int k = 0; k < CPL; ++k) x[CPL * tt + k] = 0.0f;
+            for (int k = 0; k < CPL / 2; ++k) xs[k] = make_float2(0.0f, 0.0f);
             if (tt < nt) {
-                float v[CPL];
+                float2 v[CPL / 2];
 #pragma unroll
-                for (int k = 0; k < CPL; ++k) v[k] = shared_v[buf][tt][warp * CPL + k];
+                for (int k = 0; k < CPL / 2; ++k)
+                    v[k] = make_float2(shared_v[buf][tt][warp * CPL + 2 * k], shared_v[buf][tt][warp * CPL + 2 * k + 1]);
                 float4 c[DR];       // all of the token's loads first: they do not wait for one another
 #pragma unroll
                 for (int ii = 0; ii < DR; ++ii) c[ii] = shared[buf][tt][ii * 32 + lane];
 #pragma unroll
                 for (int ii = 0; ii < DR; ++ii) {
+                    const float2 a2 = make_float2(c[ii].x, c[ii].x), k2 = make_float2(c[ii].y, c[ii].y);
+                    const float2 q2 = make_float2(c[ii].z, c[ii].z);
 #pragma unroll
-                    for (int k = 0; k < CPL; ++k) {
-                        S[ii][k] = fmaf(c[ii].x, S[ii][k], c[ii].y * v[k]);
-                        x[CPL * tt + k] = fmaf(S[ii][k], c[ii].z, x[CPL * tt + k]);
+                    for (int k = 0; k < CPL / 2; ++k) {
+                        // S <- a S + k v; x += S q (each half: fmaf(a, S, k * v) with the product rounded, as before)
+                        const float2 kv = fma2(k2, v[k], make_float2(-0.0f, -0.0f));
+                        S[ii][k] = fma2(a2, S[ii][k], kv);
+                        xs[k] = fma2(S[ii][k], q2, xs[k]);
                     }
                 }
+            }
+#pragma unroll
+            for (int k = 0; k < CPL / 2; ++k) {
+                x[CPL * tt + 2 * k] = xs[k].x;
+                x[CPL * tt + 2 * k + 1] = xs[k].y;
             }
         }
         // then one sum over the warp for all of them: at every stage a lane hands half of what it carries to the
@@ -165,7 +192,7 @@ gla_scan_kernel(const float* __restrict__ proj, int row, const float* __restrict
         const int i = ii * 32 + lane;
 #pragma unroll
         for (int c = 0; c < CPL; ++c)
-            if (i < d && j0 + c < e) s_head[(size_t)i * e + j0 + c] = S[ii][c];
+            if (i < d && j0 + c < e) s_head[(size_t)i * e + j0 + c] = (c & 1) ? S[ii][c / 2].y : S[ii][c / 2].x;
     }
 }
 
