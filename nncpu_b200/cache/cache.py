@@ -43,11 +43,16 @@ def pages_for(n_tokens: int) -> int:
 class KVRequest:
     """Keys and values of ``n_kv_heads`` heads of ``head_dim`` lanes for every
     position (``window`` 0) or for the last ``window`` positions.  ``v_head_dim``: lanes of a value head when
-    they differ from a key head's (0: the same)."""
+    they differ from a key head's (0: the same).  ``chunk`` n: queries see the keys of their own block of n positions
+    only (blocks counted from position 0), so the blocks before the one that is being filled need not be kept.
+    ``keys_only``: the mixer keeps one vector per position and head and reads it as key and as value; no value
+    pages are made, and the group's value pages are its key pages."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: int = 0
+    chunk: int = 0
+    keys_only: bool = False
 
 
 @dataclass(frozen=True)
@@ -66,14 +71,17 @@ class KVGroup:
         self.n_pages = n_pages
         shape = (len(entries), n_pages, request.n_kv_heads, PAGE)
         self.k = torch.zeros(shape + (request.head_dim,), dtype=dtype, device=device)
-        self.v = torch.zeros(shape + (request.v_head_dim or request.head_dim,), dtype=dtype, device=device)
+        self.v = self.k if request.keys_only else torch.zeros(shape + (request.v_head_dim or request.head_dim,),
+                                                              dtype=dtype, device=device)
         self.pool = IndexPool(n_pages, "cache page")
         self.tables: Dict[int, List[int]] = {}  # slot -> page ids by page index, -1 = given back
 
     def first_needed_page(self, length: int) -> int:
         """Pages below this index hold no key that a query at position
         ``length`` or later can see."""
-        w = self.request.window
+        w, c = self.request.window, self.request.chunk
+        if c > 0:
+            return (length // c * c) // PAGE        # the block that position ``length`` belongs to starts there
         if w <= 0 or length + 1 <= w:
             return 0
         return (length + 1 - w) // PAGE
@@ -99,7 +107,7 @@ class KVGroup:
                 self.pool.give_back(p)
 
     def bytes(self) -> int:
-        return (self.k.numel() + self.v.numel()) * self.k.element_size()
+        return (self.k.numel() + (0 if self.v is self.k else self.v.numel())) * self.k.element_size()
 
 
 class Cache:
@@ -139,7 +147,8 @@ class Cache:
             elif kv is not None:
                 by_request.setdefault(kv, []).append(i)
         esize = torch.empty((), dtype=dtype).element_size()
-        need = sum(len(e) * self.n_pages * kv.n_kv_heads * PAGE * (kv.head_dim + (kv.v_head_dim or kv.head_dim)) * esize
+        need = sum(len(e) * self.n_pages * kv.n_kv_heads * PAGE
+                   * (kv.head_dim + (0 if kv.keys_only else kv.v_head_dim or kv.head_dim)) * esize
                    for kv, e in by_request.items())
         for kv, entries in by_request.items():
             g = len(self.groups)
@@ -248,7 +257,7 @@ class Cache:
         for s, n in zip(slots, n_new):
             self.lengths[s] += n
             for g in self.groups:
-                if g.request.window > 0:
+                if g.request.window > 0 or g.request.chunk > 0:
                     g.trim(s, self.lengths[s])
 
     def block_table(self, group: int, slots: Sequence[int], width: Optional[int] = None) -> List[List[int]]:

@@ -2,13 +2,16 @@
 from .registry import (architectures, config_class, config_from_dict, load_config,
                        register_architecture)
 from .specs import (AttentionSpec, BlockSpec, DenseMlpSpec, EmbeddingSpec, FeedForwardSpec, GatedLinearAttentionSpec,
-                    GatedMlpSpec, MixerSpec, ModelSpec, NormSpec, OutputSpec, PositionSpec, ScheduleEntry)
+                    GatedMlpSpec, LatentAttentionSpec, MixerSpec, ModelSpec, NormSpec, OutputSpec, PositionSpec,
+                    RoutedExpertsSpec, ScheduleEntry, StreamInjection)
 from .qwen3 import Qwen3Config
 from .romepel import RomepelConfig
+from .zevivik import ZevivikConfig
 
 __all__ = [
     "architectures", "config_class", "config_from_dict", "load_config", "register_architecture",
     "AttentionSpec", "BlockSpec", "EmbeddingSpec", "FeedForwardSpec", "GatedMlpSpec", "MixerSpec",
     "ModelSpec", "NormSpec", "OutputSpec", "PositionSpec", "ScheduleEntry", "Qwen3Config", "RomepelConfig",
-    "DenseMlpSpec", "GatedLinearAttentionSpec",
+    "DenseMlpSpec", "GatedLinearAttentionSpec", "LatentAttentionSpec", "RoutedExpertsSpec", "StreamInjection",
+    "ZevivikConfig",
 ]

@@ -65,6 +65,24 @@ class AttentionSpec(MixerSpec):
     q_temp_coef: float = 0.0         # c != 0: the query at position p is multiplied by
     q_temp_every: int = 1            # 1 + c * ln(floor((p + 1) / every) + 1)
     tensor_names: str = "proj"       # "proj": <name>.q_proj.weight / .bias ...; "short": <name>.q, <name>.q.b, ... <name>.o
+    chunk: int = 0                   # n: positions are cut into blocks of n from position 0 of the sequence, and a
+                                     # query sees the keys of its own block up to itself (not together with window)
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec(MixerSpec):
+    """Attention whose keys and values are products of one latent vector per position: c = rmsnorm(W_dkv h) of
+    ``latent_dim`` lanes is all that is kept; head a has k = W_uk[a] c (``head_dim`` lanes) and v = W_uv[a] c
+    (``v_head_dim`` lanes).  No positions enter; causal; scores times ``scale``.  With ``head_gate`` every head's
+    output is multiplied by the sigmoid of one more projection of h (one logit per head)."""
+    hidden_size: int = 0
+    n_heads: int = 0
+    head_dim: int = 0
+    v_head_dim: int = 0
+    latent_dim: int = 0
+    scale: float = 0.0
+    eps: float = 1e-6
+    head_gate: bool = False
 
 
 @dataclass(frozen=True)
@@ -90,9 +108,27 @@ class FeedForwardSpec:
 
 @dataclass(frozen=True)
 class GatedMlpSpec(FeedForwardSpec):
+    """down(act(gate(x), up(x))).  ``activation`` "silu": silu(g) u; "gelu_tanh": the tanh form of GELU of g, times u;
+    "swish_clamp": with g' = min(g, limit) and u' = clamp(u, -limit, limit): g' sigmoid(1.702 g') (u' + 1)."""
     hidden_size: int = 0
     intermediate_size: int = 0
     activation: str = "silu"
+    limit: float = 0.0
+    tensor_names: str = "proj"       # "proj": <name>.gate_proj.weight ...; "short": <name>.gate, <name>.up, <name>.down
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec(FeedForwardSpec):
+    """``n_experts`` small gated feed-forwards (``<name>.e<i>.gate / .up / .down``) of which every token uses the
+    ``top`` with the largest router logits (``<name>.router`` with the bias ``<name>.router.b``, in 32-bit), weighted
+    by the softmax over the chosen logits alone; plus an optional ``shared`` gated feed-forward that every token runs."""
+    hidden_size: int = 0
+    intermediate_size: int = 0
+    n_experts: int = 0
+    top: int = 0
+    activation: str = "swish_clamp"
+    limit: float = 0.0
+    shared: Optional[GatedMlpSpec] = None
 
 
 @dataclass(frozen=True)
@@ -109,7 +145,8 @@ class BlockSpec:
     """One layer: its parts and their arrangement.  ``kind`` "prenorm":
     x += mixer(norm1(x)); x += feed_forward(norm2(x)).  ``kind`` "sandwich" norms each sublayer's output too:
     x += norm1_post(mixer(norm1(x))); x += norm2_post(feed_forward(norm2(x))), and a layer without a
-    feed-forward (``feed_forward`` None) has the first sublayer only."""
+    feed-forward (``feed_forward`` None) has the first sublayer only.  ``kind`` "parallel": both sublayers read the
+    stream as it enters the layer, x += mixer(norm1(x)) + feed_forward(norm2(x)); without a feed-forward there is no norm2."""
     kind: str
     norm1: NormSpec
     mixer: MixerSpec
@@ -120,13 +157,25 @@ class BlockSpec:
 
 
 @dataclass(frozen=True)
+class StreamInjection:
+    """What is added to the residual stream right before a schedule entry runs: with ``embedding`` the stream as the
+    embedding left it (before the first layer), and row ``row`` of the tensor ``table`` [``n_rows``, hidden]."""
+    embedding: bool = False
+    table: Optional[str] = None
+    n_rows: int = 0
+    row: int = 0
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer.  ``layer`` indexes ``ModelSpec.layers`` and may
     appear in several entries (the layer then runs again with the same
     weights and a cache of its own).  ``cache_of`` names an earlier entry
-    whose keys and values this run reads instead of keeping its own."""
+    whose keys and values this run reads instead of keeping its own.  ``inject``: what the stream receives
+    before this run (a schedule that repeats a range of layers marks the start of each pass this way)."""
     layer: int
     cache_of: Optional[int] = None
+    inject: Optional[StreamInjection] = None
 
 
 @dataclass(frozen=True)

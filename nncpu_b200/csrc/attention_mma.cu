@@ -151,7 +151,7 @@ prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     const int n_rows = min(64, q_end - q0);
     const int pos0 = tok_pos[q0];                        // positions of a sequence's new tokens are consecutive
     const int key_hi = pos0 + n_rows - 1;                // the last row's last key
-    const int key_lo = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
+    const int key_lo = first_visible_key(pos0, window);
     const int page_lo = key_lo / kPage, page_hi = key_hi / kPage;
     const int* table = block_table + (size_t)seq * bt_stride;
     const int kvh = h / (n_heads / n_kv);
@@ -165,10 +165,10 @@ prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     int lim_lo[2], lim_hi[2];
     lim_hi[0] = has_lo ? pos0 + row_lo : -1;
     lim_hi[1] = has_hi ? pos0 + row_hi : -1;
-    lim_lo[0] = (window > 0 && lim_hi[0] + 1 > window) ? lim_hi[0] + 1 - window : 0;
-    lim_lo[1] = (window > 0 && lim_hi[1] + 1 > window) ? lim_hi[1] + 1 - window : 0;
+    lim_lo[0] = first_visible_key(lim_hi[0], window);
+    lim_lo[1] = first_visible_key(lim_hi[1], window);
     const int warp_key_hi = pos0 + min(n_rows, 16 * warp + 16) - 1;   // nothing beyond this matters to the warp
-    const int warp_key_lo = (window > 0 && pos0 + 16 * warp + 1 > window) ? pos0 + 16 * warp + 1 - window : 0;
+    const int warp_key_lo = first_visible_key(pos0 + 16 * warp, window);
 
     // query fragments in the layout the instruction asks for: 4-byte loads, once per block
     uint32_t qa[HD / 16][4];
@@ -416,7 +416,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
         return;
     }
     const int pos = tok_pos[t];
-    const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    const int first = first_visible_key(pos, window);
     const int p_first = first / kPage, p_last = pos / kPage;
     const int per = (p_last - p_first + n_splits) / n_splits;      // pages per split, rounded up
     const int p0 = p_first + split * per, p1 = min(p_last, p0 + per - 1);
@@ -770,7 +770,7 @@ extern "C" int nncpu_attention_decode_mma(const void* q, const void* k_pages, co
     NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
              "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
              "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
-    NN_CHECK(n_tok >= 0 && n_splits >= 1 && n_splits <= 65535 && window >= 0, "attention decode: %d tokens, %d splits",
+    NN_CHECK(n_tok >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode: %d tokens, %d splits",
              n_tok, n_splits);
     if (scratch == nullptr && n_splits > 1)
         NN_CHECK(n_splits <= 8, "attention decode: %d splits without scratch (a cluster merges at most 8)", n_splits);
@@ -801,7 +801,7 @@ extern "C" int nncpu_attention_decode_mma_from_qkv(const float* qkv, const void*
     NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
              "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
              "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
-    NN_CHECK(n_tok >= 0 && n_splits >= 1 && n_splits <= 65535 && window >= 0, "attention decode: %d tokens, %d splits",
+    NN_CHECK(n_tok >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode: %d tokens, %d splits",
              n_tok, n_splits);
     NN_CHECK(qkv != nullptr && ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)cos_sin % 8) == 0 && ((uintptr_t)k_pages % 16) == 0 &&
                  ((uintptr_t)v_pages % 16) == 0,
@@ -841,7 +841,7 @@ extern "C" int nncpu_attention_prefill_mma(const void* q, const void* k_pages, c
     NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
              "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
              "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
-    NN_CHECK(n_tok >= 0 && n_seqs >= 0 && window >= 0, "attention prefill: %d tokens of %d sequences", n_tok, n_seqs);
+    NN_CHECK(n_tok >= 0 && n_seqs >= 0, "attention prefill: %d tokens of %d sequences", n_tok, n_seqs);
     if (n_tok == 0 || n_seqs == 0) return 0;
     if (hd == 64)
         return launch_prefill<64>(q, k_pages, v_pages, block_table, bt_stride, cu_seqlens, tok_pos, out, n_tok, n_seqs,

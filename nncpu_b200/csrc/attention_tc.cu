@@ -160,7 +160,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int n_rows = min(kQRows, q_end - q0);
     const int pos0 = p.tok_pos[q0];                  // positions of a sequence's new tokens are consecutive
     const int key_hi = pos0 + n_rows - 1;
-    const int key_lo = (p.window > 0 && pos0 + 1 > p.window) ? pos0 + 1 - p.window : 0;
+    const int key_lo = first_visible_key(pos0, p.window);
     const int page_lo = key_lo / kPage, page_hi = key_hi / kPage;
     const int n_pages = page_hi - page_lo + 1;
     const int n_steps = (n_pages + 1) / 2;           // two pages a step; the last step may hold one
@@ -334,7 +334,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const int row = quarter * 32 + lane;
         const int h = head0 + t;
         const int lim_hi = row < n_rows ? pos0 + row : -1;
-        const int lim_lo = (p.window > 0 && lim_hi + 1 > p.window) ? lim_hi + 1 - p.window : 0;
+        const int lim_lo = first_visible_key(lim_hi, p.window);
         const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(t * kStreamCols);
         // the distance bias in the unit of the unscaled scores (the scale is applied with the reference maximum)
         const float bias_per_key = p.slope_base != 0.0f
@@ -562,7 +562,7 @@ extern "C" int nncpu_attention_prefill_tc(const void* q, const void* k_pages, co
     NN_CHECK(nncpu_attention_prefill_tc_supported(n_heads, n_kv, head_dim),
              "attention (tensor cores): head size %d with %d heads over %d key/value heads is not supported "
              "(head size 64 or 128, heads a multiple of key/value heads)", head_dim, n_heads, n_kv);
-    NN_CHECK(n_tok >= 0 && n_seqs >= 0 && window >= 0 && n_pages > 0, "attention (tensor cores): %d tokens of %d sequences, %d pages",
+    NN_CHECK(n_tok >= 0 && n_seqs >= 0 && n_pages > 0, "attention (tensor cores): %d tokens of %d sequences, %d pages",
              n_tok, n_seqs, n_pages);
     NN_CHECK(((uintptr_t)q % 16) == 0 && ((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0 &&
              ((uintptr_t)out % 16) == 0, "attention (tensor cores): operands must be 16-byte aligned");

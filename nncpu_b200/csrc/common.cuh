@@ -115,6 +115,9 @@ struct NormFusion {
 };
 
 constexpr int kActNone = 0, kActXielu = 1;
+// with the gated epilogue (act(gate) * up; kActNone there is silu(g) u): the tanh form of GELU, and the clamped
+// g sigmoid(1.702 g) (u + 1) with its limit in act_a
+constexpr int kActGateGelu = 2, kActGateSwishClamp = 3;
 
 // xIELU: a z^2 + z / 2 above zero, b (exp(z) - 1 - z) + z / 2 below, with a = softplus(p), b = 1/2 + softplus(q).
 __device__ __forceinline__ float xielu_f(float z, float a, float b) {
@@ -149,6 +152,37 @@ __device__ __forceinline__ float bins_total(const unsigned long long* bins) {
         s += (__ull2float_rn(bins[b]) * c) * c;
     }
     return s;
+}
+
+// The first key that the query at position `pos` sees, for every attention kernel.  span > 0: a sliding window, the
+// last `span` keys up to the query; span < 0: blocks of -span positions counted from position 0 of the sequence, and
+// a query sees the keys of its own block up to itself; 0: every key up to the query.  It never decreases with pos.
+__device__ __forceinline__ int first_visible_key(int pos, int span) {
+    if (span > 0) return pos + 1 > span ? pos + 1 - span : 0;
+    if (span < 0 && pos > 0) return (pos / (0 - span)) * (0 - span);
+    return 0;
+}
+
+// Gated activations act(gate) * up of the feed-forwards, on 32-bit values.  kGateSilu: silu(g) u.  kGateGeluTanh: the
+// tanh form of GELU, g/2 (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) u.  kGateSwishClamp: with g' = min(g, limit) and
+// u' = clamp(u, -limit, limit): g' sigmoid(1.702 g') (u' + 1).
+constexpr int kGateSilu = 0, kGateGeluTanh = 1, kGateSwishClamp = 2;
+__device__ __forceinline__ float gated_act_f(float g, float u, int kind, float limit) {
+    if (kind == kGateGeluTanh) {
+        const float inner = 0.7978845608028654f * fmaf(0.044715f * g * g, g, g);
+        return (0.5f * g * (1.0f + tanhf(inner))) * u;
+    }
+    if (kind == kGateSwishClamp) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, 0.0f - limit), limit);
+        return (g * (1.0f / (1.0f + expf(-1.702f * g)))) * (u + 1.0f);
+    }
+    return (g * (1.0f / (1.0f + expf(0.0f - g)))) * u;
+}
+
+// The gated epilogue's activation by a product's `act` code.
+__device__ __forceinline__ float gated_epilogue_f(float g, float u, int act, float act_a) {
+    return gated_act_f(g, u, act == kActGateGelu ? kGateGeluTanh : (act == kActGateSwishClamp ? kGateSwishClamp : kGateSilu), act_a);
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -55,7 +55,6 @@ enum GemmStatus : int { kOk = 0, kTimeoutEmpty = 101, kTimeoutFull = 102, kTimeo
                         kTimeoutAccumEmpty = 104 };
 enum Epilogue : int { kPlain = 0, kSwiglu = 1, kQkv = 2 };
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return (g * (1.0f / (1.0f + expf(0.0f - g)))) * u; }
 
 // What the fused q/k/v epilogue needs: the output columns are heads of 128 (queries, then keys, then values).
 struct QkvParams {
@@ -104,7 +103,7 @@ __device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, 
             const size_t o = (size_t)a_row * p.ldc + (b0 >> 1);
             float act[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) act[j] = silu_mul(v[j], v[j + 8]);
+            for (int j = 0; j < 8; ++j) act[j] = gated_epilogue_f(v[j], v[j + 8], p.nf.act, p.nf.act_a);
             if (p.vec && p.out_dt == DT_BF16) {
                 __nv_bfloat162 h[4];
 #pragma unroll
@@ -128,7 +127,7 @@ __device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, 
                 const int jj = is_gate ? j : j + 1;
                 const int tok = b0 + jj;
                 if (a_ok && jj < ncols && tok < p.rows_b)
-                    st_f(p.out, (size_t)tok * p.ldc + feature, p.out_dt, silu_mul(g, u));
+                    st_f(p.out, (size_t)tok * p.ldc + feature, p.out_dt, gated_epilogue_f(g, u, p.nf.act, p.nf.act_a));
             }
         }
         return;
@@ -1723,8 +1722,9 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
         p.nf.bins_in = (const unsigned long long*)bins_in;
         p.nf.eps = eps;
     }
-    NN_CHECK(act == kActNone || (act == kActXielu && epilogue == kPlain && !accumulate && xg_out == nullptr),
-             "gemm: an activation (%d) goes with the plain epilogue, without accumulation or a norm after it", act);
+    NN_CHECK(act == kActNone || (act == kActXielu && epilogue == kPlain && !accumulate && xg_out == nullptr) ||
+                 ((act == kActGateGelu || act == kActGateSwishClamp) && epilogue == kSwiglu),
+             "gemm: activation %d goes with the plain epilogue (without accumulation or a norm after it) or, as a gate, with the gated one", act);
     p.nf.act = act; p.nf.act_a = act_a; p.nf.act_b = act_b;
     CUtensorMap ma, mb;
     int bn;

@@ -543,7 +543,8 @@ extern "C" int nncpu_qk_norm_rope_append(const void* qkv, int in_dt, const void*
 
 // ---------------------------------------------------------------------------
 // Attention of every (token, head) over the cache of the token's sequence:
-// keys first..pos with first = max(0, pos + 1 - window) (window 0: all).
+// keys first..pos with first = first_visible_key(pos, window): a sliding window (window > 0), blocks of
+// -window positions (window < 0) or every earlier key (0).
 // One block per (token, head) walks the span in chunks of 128 keys with an
 // online softmax; the chunk boundaries are fixed by the span alone, so the
 // result does not depend on the batch or on how tokens were cut into steps.
@@ -573,7 +574,7 @@ attention_kernel(const void* __restrict__ q, int q_dt, const void* __restrict__ 
     }
     const float slope = slope_base != 0.0f ? exp2f(-slope_base * (float)(h + 1) / (float)n_heads) : 0.0f;
     const int pos = tok_pos[t];
-    const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    const int first = first_visible_key(pos, window);
     const int kvh = h / (n_heads / n_kv);
     for (int d = tid; d < hd; d += kAttnThreads) qs[d] = ld_f(q, q_base + d, q_dt);
     __syncthreads();
@@ -630,7 +631,6 @@ extern "C" int nncpu_attention(const void* q, int q_dt, const void* k_pages, con
              "attention: %d heads over %d key/value heads", n_heads, n_kv);
     NN_CHECK(hd > 0 && hd <= 1024, "attention: head size %d must be positive and at most 1024", hd);
     NN_CHECK(vd > 0 && vd <= 1024, "attention: value size %d must be positive and at most 1024", vd);
-    NN_CHECK(window >= 0, "attention: window %d", window);
     if (n_tok == 0) return 0;
     const size_t smem = (hd + kAttnThreads) * sizeof(float) + kAttnThreads * sizeof(long long) + 8;
     dim3 grid(n_tok, n_heads);
@@ -643,26 +643,29 @@ extern "C" int nncpu_attention(const void* q, int q_dt, const void* k_pages, con
 }
 
 // ---------------------------------------------------------------------------
-// Gated activation: out[t, i] = silu(gu[t, i]) * gu[t, inter + i].
+// Gated activation: out[t, i] = act(gu[t, i], gu[t, inter + i]) with act one of gated_act_f's kinds
+// (silu(g) u; the tanh form of GELU times u; the clamped g sigmoid(1.702 g) (u + 1)), in 32-bit.
 // ---------------------------------------------------------------------------
-__global__ void swiglu_kernel(const void* __restrict__ gu, int in_dt, void* __restrict__ out, int out_dt,
-                              long n_tok, int inter) {
+__global__ void gated_act_kernel(const void* __restrict__ gu, int in_dt, void* __restrict__ out, int out_dt,
+                                 long n_tok, int inter, int kind, float limit) {
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n_tok * inter) return;
     const long t = idx / inter;
     const int i = (int)(idx % inter);
     const float g = ld_f(gu, (size_t)t * 2 * inter + i, in_dt);
     const float u = ld_f(gu, (size_t)t * 2 * inter + inter + i, in_dt);
-    st_f(out, (size_t)idx, out_dt, (g * (1.0f / (1.0f + expf(0.0f - g)))) * u);
+    st_f(out, (size_t)idx, out_dt, gated_act_f(g, u, kind, limit));
 }
 
-extern "C" int nncpu_swiglu(const void* gu, int in_dt, void* out, int out_dt, int n_tok, int inter, void* stream) {
-    NN_CHECK(n_tok >= 0 && inter > 0, "swiglu: %d tokens of %d", n_tok, inter);
+extern "C" int nncpu_gated_act(const void* gu, int in_dt, void* out, int out_dt, int n_tok, int inter, int kind,
+                               float limit, void* stream) {
+    NN_CHECK(n_tok >= 0 && inter > 0, "gated activation: %d tokens of %d", n_tok, inter);
+    NN_CHECK(kind >= kGateSilu && kind <= kGateSwishClamp, "gated activation: kind %d", kind);
     if (n_tok == 0) return 0;
     const long total = (long)n_tok * inter;
-    swiglu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gu, in_dt, out, out_dt, n_tok,
-                                                                                      inter);
-    NN_LAUNCH_OK("swiglu");
+    gated_act_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gu, in_dt, out, out_dt, n_tok,
+                                                                                         inter, kind, limit);
+    NN_LAUNCH_OK("gated activation");
     return 0;
 }
 
@@ -1525,5 +1528,336 @@ extern "C" int nncpu_sample_temperature(const float* logits, const double* u, in
     }
     sample_kernel<<<n_rows, 1024, 0, stream>>>(logits, u, out, vocab, 1.0f / temperature);
     NN_LAUNCH_OK("sample");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// x[t, :] += rows[t, :] + vec[:]: what a schedule adds to the residual stream
+// before a run of layers (an earlier state of the stream, a learned vector).
+// Either addend may be null.  32-bit.
+// ---------------------------------------------------------------------------
+__global__ void stream_add_kernel(float* __restrict__ x, const float* __restrict__ rows, const void* __restrict__ vec,
+                                  int vec_dt, long total, int dim) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    float v = x[idx];
+    if (rows) v += rows[idx];
+    if (vec) v += ld_f(vec, (size_t)(idx % dim), vec_dt);
+    x[idx] = v;
+}
+
+extern "C" int nncpu_stream_add(float* x, const float* rows, const void* vec, int vec_dt, int n_tok, int dim,
+                                void* stream) {
+    NN_CHECK(n_tok >= 0 && dim > 0, "stream add: %d rows of %d", n_tok, dim);
+    if (n_tok == 0 || (rows == nullptr && vec == nullptr)) return 0;
+    const long total = (long)n_tok * dim;
+    stream_add_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, rows, vec, vec_dt, total, dim);
+    NN_LAUNCH_OK("stream add");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Two norms of the same rows in one pass (a layer whose sublayers both read the
+// stream as it enters the layer): y1 = x * scale1 * gamma1, y2 = x * scale2 * gamma2
+// with scale = 1 / sqrt(mean(x^2) + eps).  x float32; the sum of squares is taken once.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+rmsnorm_dual_kernel(const float* __restrict__ x, const void* __restrict__ g1, const void* __restrict__ g2, int g_dt,
+                    float eps1, float eps2, void* __restrict__ y1, void* __restrict__ y2, int y_dt, int dim) {
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * dim;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = x[base + i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float mean = ss * (1.0f / (float)dim);
+    const float s1 = 1.0f / sqrtf(mean + eps1), s2 = 1.0f / sqrtf(mean + eps2);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = x[base + i];
+        st_f(y1, base + i, y_dt, (v * s1) * ld_f(g1, i, g_dt));
+        st_f(y2, base + i, y_dt, (v * s2) * ld_f(g2, i, g_dt));
+    }
+}
+
+extern "C" int nncpu_rmsnorm_dual(const float* x, const void* g1, const void* g2, int g_dt, float eps1, float eps2,
+                                  void* y1, void* y2, int y_dt, int n_rows, int dim, void* stream) {
+    NN_CHECK(n_rows >= 0 && dim > 0, "rmsnorm (two outputs): %d rows of %d", n_rows, dim);
+    if (n_rows == 0) return 0;
+    rmsnorm_dual_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>(x, g1, g2, g_dt, eps1, eps2, y1, y2, y_dt, dim);
+    NN_LAUNCH_OK("rmsnorm (two outputs)");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// One small product per head: C[m, b, :] = A[m, b, :] . W[b]^T for b < n_batch, with A [M, lda] holding head b's
+// K lanes at column b * a_step, W [n_batch, N, K] and C [M, ldc] taking head b's N lanes at column b * c_step.
+// With `gate` [M, gate_ld] (32-bit logits) row m of head b is multiplied by sigmoid(gate[m, gate_col + b]).
+// 32-bit multiply-add on CUDA cores, k ascending per output element.
+// ---------------------------------------------------------------------------
+template <int BM, int BN, int BK, int TM, int TN>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+linear_heads_kernel(const void* __restrict__ A, int a_dt, const void* __restrict__ W, int w_dt, void* __restrict__ C,
+                    int c_dt, int M, int N, int K, int lda, int ldc, int a_step, int c_step,
+                    const float* __restrict__ gate, int gate_ld, int gate_col) {
+    constexpr int NT = (BM / TM) * (BN / TN);
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    const int tid = threadIdx.x, b = blockIdx.z;
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const size_t a0 = (size_t)b * a_step, w0 = (size_t)b * N * K, c0 = (size_t)b * c_step;
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int e = tid; e < BM * BK; e += NT) {
+            const int r = e / BK, c = e % BK;
+            const int m = m0 + r, k = k0 + c;
+            As[c][r] = (m < M && k < K) ? ld_f(A, a0 + (size_t)m * lda + k, a_dt) : 0.0f;
+        }
+        for (int e = tid; e < BN * BK; e += NT) {
+            const int r = e / BK, c = e % BK;
+            const int n = n0 + r, k = k0 + c;
+            Ws[c][r] = (n < N && k < K) ? ld_f(W, w0 + (size_t)n * K + k, w_dt) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[TM], w[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) w[j] = Ws[kk][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int m = m0 + ty * TM + i;
+        if (m >= M) continue;
+        const float g = gate ? 1.0f / (1.0f + expf(0.0f - gate[(size_t)m * gate_ld + gate_col + b])) : 1.0f;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + tx * TN + j;
+            if (n < N) st_f(C, c0 + (size_t)m * ldc + n, c_dt, acc[i][j] * g);
+        }
+    }
+}
+
+extern "C" int nncpu_linear_heads(const void* A, int a_dt, const void* W, int w_dt, void* C, int c_dt, int M, int N,
+                                  int K, int n_batch, int lda, int ldc, int a_step, int c_step, const float* gate,
+                                  int gate_ld, int gate_col, void* stream) {
+    NN_CHECK(M >= 0 && N > 0 && K > 0 && n_batch > 0 && n_batch <= 65535, "per-head product: M %d, N %d, K %d, %d heads",
+             M, N, K, n_batch);
+    NN_CHECK(lda >= (n_batch - 1) * a_step + K && ldc >= (n_batch - 1) * c_step + N && a_step >= 0 && c_step >= N,
+             "per-head product: row strides %d / %d for %d heads of %d / %d lanes", lda, ldc, n_batch, K, N);
+    NN_CHECK(gate == nullptr || gate_ld >= gate_col + n_batch, "per-head product: gate stride %d", gate_ld);
+    if (M == 0) return 0;
+    if (M <= 16) {
+        dim3 grid((N + 63) / 64, (M + 15) / 16, n_batch);
+        linear_heads_kernel<16, 64, 32, 2, 2><<<grid, 256, 0, (cudaStream_t)stream>>>(
+            A, a_dt, W, w_dt, C, c_dt, M, N, K, lda, ldc, a_step, c_step, gate, gate_ld, gate_col);
+    } else {
+        dim3 grid((N + 63) / 64, (M + 63) / 64, n_batch);
+        NN_CHECK(grid.y <= 65535, "per-head product: %d rows", M);
+        linear_heads_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, (cudaStream_t)stream>>>(
+            A, a_dt, W, w_dt, C, c_dt, M, N, K, lda, ldc, a_step, c_step, gate, gate_ld, gate_col);
+    }
+    NN_LAUNCH_OK("per-head product");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Latent attention keeps one vector per position: c = rmsnorm(z) * gamma of `rank` lanes, where z sits at column
+// `col` of the rows of proj [n_tok, ld] (32-bit).  It goes to the token's row of the key pages (one key/value head
+// of `rank` lanes); the same pages serve as values.  One block per token.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+latent_append_kernel(const float* __restrict__ proj, int ld, int col, const void* __restrict__ gamma, int g_dt,
+                     float eps, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                     const int* __restrict__ block_table, int bt_stride, void* __restrict__ pages, int kv_dt,
+                     int rank) {
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const int seq = tok_seq[t];
+    if (seq < 0) return;                    // a padded row owns no place in the cache
+    const float* z = proj + (size_t)t * ld + col;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) ss = fmaf(z[i], z[i], ss);
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss * (1.0f / (float)rank) + eps);
+    const int pos = tok_pos[t];
+    const int page = block_table[(size_t)seq * bt_stride + pos / kPage];
+    if (page < 0) return;
+    const size_t o = ((size_t)page * kPage + pos % kPage) * rank;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) st_f(pages, o + i, kv_dt, (z[i] * scale) * ld_f(gamma, i, g_dt));
+}
+
+extern "C" int nncpu_latent_append(const float* proj, int ld, int col, const void* gamma, int g_dt, float eps,
+                                   const int* tok_seq, const int* tok_pos, const int* block_table, int bt_stride,
+                                   void* pages, int kv_dt, int n_tok, int rank, void* stream) {
+    NN_CHECK(n_tok >= 0 && rank > 0 && col >= 0 && ld >= col + rank, "latent append: %d tokens, rank %d at column %d of %d",
+             n_tok, rank, col, ld);
+    if (n_tok == 0) return 0;
+    latent_append_kernel<<<n_tok, 128, 0, (cudaStream_t)stream>>>(proj, ld, col, gamma, g_dt, eps, tok_seq, tok_pos,
+                                                                  block_table, bt_stride, pages, kv_dt, rank);
+    NN_LAUNCH_OK("latent append");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Routed experts.
+//   route: per token the `top` largest of its n_experts router logits (the lower index wins a tie), in descending
+//     order, and the softmax over those logits alone.  One warp per token, 32-bit.
+//   gate/up: for slot s = (token t, choice c) with expert e: act[s, j] = gated_act(Wg[e, j] . h_t, Wu[e, j] . h_t).
+//   down: out[t, i] += sum_c weight[t, c] * (Wd[e_c, i] . act[(t, c)]), choices added in their order.
+// The two products keep a warp on an output feature, lanes across k, and add in a fixed order, so a token's result
+// does not depend on the batch.  They serve every size and element type; weights are [n_experts, rows, cols].
+// ---------------------------------------------------------------------------
+constexpr int kRouteMaxExperts = 1024;
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int n_tok, int n_experts, int top, int* __restrict__ ids,
+                 float* __restrict__ weights) {
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= n_tok) return;
+    float* z = smem + (size_t)warp * n_experts;
+    for (int e = lane; e < n_experts; e += 32) z[e] = logits[(size_t)t * n_experts + e];
+    __syncwarp();
+    float z_first = 0.0f, sum = 0.0f;
+    for (int c = 0; c < top; ++c) {
+        float best = -INFINITY;
+        int at = n_experts;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float v = z[e];
+            if (v > best || (v == best && e < at)) { best = v; at = e; }   // NaN never wins; -inf only by index order
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (at >= n_experts) at = 0;            // nothing but NaN is left: garbage in, an expert that exists out
+        if (c == 0) z_first = best;
+        const float w = expf(best - z_first);
+        sum += w;
+        if (lane == 0) {
+            ids[(size_t)t * top + c] = at;
+            weights[(size_t)t * top + c] = w;
+            z[at] = __int_as_float(0x7FC00000);   // taken: NaN loses every comparison above
+        }
+        __syncwarp();
+    }
+    const float inv = 1.0f / sum;
+    for (int c = lane; c < top; c += 32) weights[(size_t)t * top + c] *= inv;
+}
+
+extern "C" int nncpu_moe_route(const float* logits, int n_tok, int n_experts, int top, int* ids, float* weights,
+                               void* stream) {
+    NN_CHECK(n_tok >= 0 && n_experts > 0 && n_experts <= kRouteMaxExperts && top > 0 && top <= n_experts,
+             "router: %d tokens, the top %d of %d experts (at most %d)", n_tok, top, n_experts, kRouteMaxExperts);
+    if (n_tok == 0) return 0;
+    const size_t smem = (size_t)4 * n_experts * sizeof(float);
+    moe_route_kernel<<<(n_tok + 3) / 4, 128, smem, (cudaStream_t)stream>>>(logits, n_tok, n_experts, top, ids, weights);
+    NN_LAUNCH_OK("router");
+    return 0;
+}
+
+// A warp's dot product of a weight row with a vector held in shared memory as floats.
+__device__ __forceinline__ float warp_dot(const void* __restrict__ w, size_t row_at, int w_dt, const float* __restrict__ x,
+                                          int k, int lane) {
+    float acc = 0.0f;
+    if (w_dt == DT_BF16 && (k & 7) == 0) {
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(w) + row_at);
+        for (int i = lane; i < (k >> 3); i += 32) {
+            const uint4 v = src[i];
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+            const float* xs = x + 8 * i;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(h[j]);
+                acc = fmaf(f.x, xs[2 * j], acc);
+                acc = fmaf(f.y, xs[2 * j + 1], acc);
+            }
+        }
+    } else {
+        for (int i = lane; i < k; i += 32) acc = fmaf(ld_f(w, row_at + i, w_dt), x[i], acc);
+    }
+    return warp_sum(acc);
+}
+
+constexpr int kMoeWarps = 8;
+
+__global__ void __launch_bounds__(kMoeWarps * 32)
+moe_gate_up_kernel(const void* __restrict__ x, int x_dt, const void* __restrict__ wg, const void* __restrict__ wu,
+                   int w_dt, const int* __restrict__ ids, void* __restrict__ act, int act_dt, int top, int width, int ff,
+                   int n_experts, int kind, float limit) {
+    extern __shared__ float smem[];          // the token's input as floats
+    const int s = blockIdx.x, t = s / top;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = ids[s];
+    for (int i = threadIdx.x; i < width; i += blockDim.x) smem[i] = ld_f(x, (size_t)t * width + i, x_dt);
+    __syncthreads();
+    if (e < 0 || e >= n_experts) return;
+    const size_t w0 = (size_t)e * ff * width;
+    for (int j = blockIdx.y * kMoeWarps + warp; j < ff; j += gridDim.y * kMoeWarps) {
+        const float g = warp_dot(wg, w0 + (size_t)j * width, w_dt, smem, width, lane);
+        const float u = warp_dot(wu, w0 + (size_t)j * width, w_dt, smem, width, lane);
+        if (lane == 0) st_f(act, (size_t)s * ff + j, act_dt, gated_act_f(g, u, kind, limit));
+    }
+}
+
+__global__ void __launch_bounds__(kMoeWarps * 32)
+moe_down_kernel(const void* __restrict__ act, int act_dt, const void* __restrict__ wd, int w_dt,
+                const int* __restrict__ ids, const float* __restrict__ weights, float* __restrict__ out, int top,
+                int width, int ff, int n_experts) {
+    extern __shared__ float smem[];          // the token's top * ff activations as floats
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < top * ff; i += blockDim.x) smem[i] = ld_f(act, (size_t)t * top * ff + i, act_dt);
+    __syncthreads();
+    for (int i = blockIdx.y * kMoeWarps + warp; i < width; i += gridDim.y * kMoeWarps) {
+        float sum = 0.0f;
+        for (int c = 0; c < top; ++c) {
+            const int e = ids[(size_t)t * top + c];
+            if (e < 0 || e >= n_experts) continue;
+            const float d = warp_dot(wd, ((size_t)e * width + i) * ff, w_dt, smem + (size_t)c * ff, ff, lane);
+            sum = fmaf(weights[(size_t)t * top + c], d, sum);
+        }
+        if (lane == 0) out[(size_t)t * width + i] += sum;
+    }
+}
+
+extern "C" int nncpu_moe_experts(const void* x, int x_dt, const void* wg, const void* wu, const void* wd, int w_dt,
+                                 const int* ids, const float* weights, void* act, int act_dt, float* out, int n_tok,
+                                 int top, int width, int ff, int n_experts, int kind, float limit, void* stream) {
+    NN_CHECK(n_tok >= 0 && top > 0 && width > 0 && ff > 0 && n_experts > 0, "experts: %d tokens, top %d, %d x %d, %d experts",
+             n_tok, top, width, ff, n_experts);
+    NN_CHECK(kind >= kGateSilu && kind <= kGateSwishClamp, "experts: activation kind %d", kind);
+    NN_CHECK((size_t)width * 4 <= 48 * 1024 && (size_t)top * ff * 4 <= 48 * 1024,
+             "experts: a token's %d inputs or %d x %d activations do not fit the shared memory of this kernel", width, top, ff);
+    if (n_tok == 0) return 0;
+    const long slots = (long)n_tok * top;
+    NN_CHECK(slots < (1l << 31), "experts: %ld token slots", slots);
+    // few tokens: more blocks per token, so that the weights' stream is spread over the SMs
+    const int split_up = (int)max(1l, min((long)(ff + kMoeWarps - 1) / kMoeWarps, 1024 / max(1l, slots)));
+    const int split_down = (int)max(1l, min((long)(width + kMoeWarps - 1) / kMoeWarps, 1024 / max(1l, (long)n_tok)));
+    moe_gate_up_kernel<<<dim3((unsigned)slots, split_up), kMoeWarps * 32, (size_t)width * 4, (cudaStream_t)stream>>>(
+        x, x_dt, wg, wu, w_dt, ids, act, act_dt, top, width, ff, n_experts, kind, limit);
+    NN_LAUNCH_OK("experts (gate and up)");
+    moe_down_kernel<<<dim3(n_tok, split_down), kMoeWarps * 32, (size_t)top * ff * 4, (cudaStream_t)stream>>>(
+        act, act_dt, wd, w_dt, ids, weights, out, top, width, ff, n_experts);
+    NN_LAUNCH_OK("experts (down)");
     return 0;
 }

@@ -70,7 +70,6 @@ __device__ __forceinline__ uint4 ldg16_stream(const __nv_bfloat16* p) {
     return __ldcs(reinterpret_cast<const uint4*>(p));
 }
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return (g * (1.0f / (1.0f + expf(0.0f - g)))) * u; }
 
 // NT = number of 8-token tiles (1: up to 8 tokens, 2: up to 16); kW = warps of the block (8 or 4).
 template <int NT, int kEpi, int kW>
@@ -227,7 +226,7 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
                 g *= row_scale[tok];
                 u *= row_scale[tok];
             }
-            st_f(out, (size_t)tok * ldc + (row0 >> 1) + j, out_dt, silu_mul(g, u));
+            st_f(out, (size_t)tok * ldc + (row0 >> 1) + j, out_dt, gated_epilogue_f(g, u, nf.act, nf.act_a));
         }
     } else {
         // output element i is (token i / 16, row i % 16): one per thread of 8 warps, two per thread of 4; every thread
@@ -348,8 +347,9 @@ extern "C" int nncpu_linear_skinny(const void* X, const void* W, const void* bia
     const int n_out = epilogue == kSwiglu ? N / 2 : N;
     NN_CHECK(ldc >= n_out, "linear (few tokens): ldc %d is below the %d output features", ldc, n_out);
     NormFusion nf{};
-    NN_CHECK(act == kActNone || (act == kActXielu && epilogue == kPlain && !accumulate && xg_out == nullptr),
-             "linear (few tokens): an activation (%d) goes with the plain epilogue, without accumulation or a norm after it", act);
+    NN_CHECK(act == kActNone || (act == kActXielu && epilogue == kPlain && !accumulate && xg_out == nullptr) ||
+                 ((act == kActGateGelu || act == kActGateSwishClamp) && epilogue == kSwiglu),
+             "linear (few tokens): activation %d goes with the plain epilogue (without accumulation or a norm after it) or, as a gate, with the gated one", act);
     nf.act = act; nf.act_a = act_a; nf.act_b = act_b;
     if (xg_out != nullptr) {
         NN_CHECK(epilogue == kPlain && gamma != nullptr && bins_out != nullptr && ((uintptr_t)bins_out % 8) == 0 &&

@@ -55,6 +55,17 @@ def _shares(spec: ModelSpec) -> List[bool]:
     return [bool(s) for s in share]
 
 
+def _injected_tables(spec: ModelSpec) -> Dict[str, int]:
+    """Tensors whose rows the schedule adds to the stream (``ScheduleEntry.inject``): name -> rows."""
+    tables: Dict[str, int] = {}
+    for i, e in enumerate(spec.schedule):
+        if e.inject is not None and e.inject.table is not None:
+            inj = e.inject
+            if not 0 <= inj.row < inj.n_rows or tables.setdefault(inj.table, inj.n_rows) != inj.n_rows:
+                raise BadFormat(f"schedule entry {i} adds row {inj.row} of {inj.table!r}, a table of {inj.n_rows} rows")
+    return tables
+
+
 def build_blocks(spec: ModelSpec) -> list:
     shares = _shares(spec)
     return [build("block", b, **({"reads_other_cache": True} if shares[i] else {}))
@@ -67,6 +78,8 @@ def parameter_list(spec: ModelSpec) -> List[ParamSpec]:
     params = [ParamSpec(e.name + e.suffix, (e.vocab_size, e.hidden_size))]
     if e.positions is not None:
         params.append(ParamSpec(e.positions, (e.n_positions, e.hidden_size)))
+    for table, n_rows in _injected_tables(spec).items():
+        params.append(ParamSpec(table, (n_rows, spec.hidden_size), init=("normal", 0.5)))
     for block in build_blocks(spec):
         params += block.params()
     params += build("norm", o.norm).params()
@@ -90,6 +103,10 @@ class Model:
         # learned position vectors, added to the embedding rows: sequences cannot grow beyond the table
         self.pos_table = None if spec.embedding.positions is None else tensors[spec.embedding.positions]
         self.lm_head = self.embed_table if spec.output.tied else tensors[spec.output.name + spec.output.suffix]
+        # what the schedule adds to the stream before some of its entries: rows of learned tables, and the stream as
+        # the embedding left it (kept for the step only if some entry asks for it)
+        self.injected = {name: tensors[name] for name in _injected_tables(spec)}
+        self.keeps_embedding = any(e.inject is not None and e.inject.embedding for e in spec.schedule)
         for block in self.blocks:
             block.bind(tensors, rt)
         self.final_norm.bind(tensors, rt)
@@ -174,12 +191,22 @@ class Model:
         residual = rt.empty(ctx.n_tokens, spec.hidden_size, dtype=torch.float32)
         with rt.phase("embed"):
             ops.embed(self.embed_table, ctx.tok_ids, residual, spec.embedding.scale, self.pos_table, ctx.tok_pos)
+        first_stream = None
+        if self.keeps_embedding:
+            first_stream = rt.empty(ctx.n_tokens, spec.hidden_size, dtype=torch.float32, keep=True)
+            with rt.phase("embed"):
+                ops.embed(self.embed_table, ctx.tok_ids, first_stream, spec.embedding.scale, self.pos_table, ctx.tok_pos)
         ctx.next_norm = ctx.after_block = None
         fusing = rt.dtype == torch.bfloat16 and rt.fuses_norms(ctx.n_tokens, spec.hidden_size)
         if fusing:
             rt.begin_norm_fusion(ctx.n_tokens)      # norms may ride on the products around them
         for i, (e, (first, count)) in enumerate(zip(self.schedule, self._users)):
-            if i + 1 < len(self.schedule):
+            if e.inject is not None:
+                ctx.next_norm = None            # the stream changes before the block's first norm reads it
+                with rt.phase("embed"):
+                    ops.stream_add(residual, first_stream if e.inject.embedding else None,
+                                   None if e.inject.table is None else self.injected[e.inject.table][e.inject.row])
+            if i + 1 < len(self.schedule) and self.schedule[i + 1].inject is None:
                 # the block that follows may ask this one to leave its first norm's input (a few tokens only)
                 ctx.after_block = self.blocks[self.schedule[i + 1].layer].entry_norm_request(ctx, residual)
             self.blocks[e.layer].forward(ctx, residual, [ctx.entry_cache(cache, u) for u in range(first, first + count)])

@@ -47,10 +47,10 @@ class StepContext:
     after_block: Optional[object] = None  # the request of the block that follows, for the running block's last part
     branch_is_fresh: bool = False         # the "residual" a part was given is an uninitialised branch: its last product writes, not adds
 
-    def span_sum(self, window: int = 0) -> int:
+    def span_sum(self, window: int = 0, chunk: int = 0) -> int:
         """Keys that the step's tokens attend to, summed over the tokens: a token at position p sees p + 1
-        keys, or the last ``window`` of them."""
-        key = ("span_sum", window)
+        keys, or the last ``window`` of them, or the p % chunk + 1 of its own block of ``chunk`` positions."""
+        key = ("span_sum", window, chunk)
         n = self.memo.get(key)
         if n is None:
             n = 0
@@ -58,6 +58,8 @@ class StepContext:
                 first = after - q + 1                      # keys seen by the sequence's first new token
                 if window > 0:
                     n += sum(min(first + i, window) for i in range(q))
+                elif chunk > 0:
+                    n += sum((first - 1 + i) % chunk + 1 for i in range(q))
                 else:
                     n += q * first + q * (q - 1) // 2
             self.memo[key] = n

@@ -193,15 +193,20 @@ PLANS = {"auto": 0, "even_from_17": 1, "never_even": 2, "no_pairs": 4, "narrow_u
 EPILOGUES = {"plain": 0, "swiglu": 1}
 
 
+_ACTIVATIONS = {"xielu": 1, "gelu_tanh": 2, "swish_clamp": 3}
+
+
 def _activation(activation):
-    """``activation`` None, or ("xielu", a, b) with a = softplus(p) and b = 1/2 + softplus(q) ready-made: applied to
-    the product's result after the bias (plain epilogue, no accumulation)."""
+    """``activation`` None, or (kind, a, b).  With the plain epilogue ("xielu", a, b), a = softplus(p) and
+    b = 1/2 + softplus(q) ready-made: applied to the product's result after the bias (no accumulation).  With the
+    gated epilogue the gate's activation in place of SiLU: ("gelu_tanh", 0, 0) or ("swish_clamp", limit, 0), see
+    ``gated_act``."""
     if activation is None:
         return _i(0), _f(0.0), _f(0.0)
     kind, a, b = activation
-    if kind != "xielu":
+    if kind not in _ACTIVATIONS:
         raise InvalidArgument(f"a product cannot apply the activation {kind!r}")
-    return _i(1), _f(a), _f(b)
+    return _i(_ACTIVATIONS[kind]), _f(a), _f(b)
 
 
 @functools.lru_cache(maxsize=4096)
@@ -371,9 +376,19 @@ def qk_norm_rope_append(qkv, q_gamma, k_gamma, eps, cos_sin, tok_seq, tok_pos, b
           _i(n_heads), _i(n_kv), _i(head_dim), _i(v_head_dim), _f(coef), _i(every), _stream())
 
 
+def key_span(window: int = 0, chunk: int = 0) -> int:
+    """The one number by which every attention kernel knows which earlier keys a query sees (their ``window``
+    argument): ``window`` > 0, the last ``window`` keys up to the query, as it is; ``chunk`` > 0, the keys of the
+    query's own block of ``chunk`` positions (blocks counted from position 0 of the sequence), as ``-chunk``; 0: all."""
+    if window < 0 or chunk < 0 or (window and chunk):
+        raise InvalidArgument(f"a mixer's keys are limited by a window ({window}) or by blocks ({chunk}), not both")
+    return window if window else -chunk
+
+
 def attention(q, k_pages, v_pages, block_table, tok_seq, tok_pos, out, n_heads: int, n_kv: int, head_dim: int,
               scale: float, window: int = 0, v_head_dim: int = 0, slope_base: float = 0.0) -> None:
-    """Causal attention of each token over its sequence's pages.  ``v_head_dim``: lanes of a value head (and of
+    """Causal attention of each token over its sequence's pages.  ``window``: see ``key_span`` (here and in the
+    other attention kernels).  ``v_head_dim``: lanes of a value head (and of
     the output) when they differ from ``head_dim``.  ``slope_base`` b != 0: head h takes
     2^(-b (h + 1) / n_heads) * (query position - key position) off its scaled scores."""
     n = q.shape[0]
@@ -485,12 +500,89 @@ def attention_prefill_tc(q, k_pages, v_pages, block_table, cu_seqlens, tok_pos, 
           _i(n_heads), _i(n_kv), _i(head_dim), _f(scale), _i(window), _f(slope_base), _ptr(status), _stream())
 
 
-def swiglu(gate_up, out) -> None:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+GATED_ACTS = {"silu": 0, "gelu_tanh": 1, "swish_clamp": 2}
+
+
+def gated_act(gate_up, out, kind: str = "silu", limit: float = 0.0) -> None:
+    """out[t, i] = act(gate_up[t, i], gate_up[t, I + i]) in 32-bit.  ``kind`` "silu": silu(g) u; "gelu_tanh":
+    g/2 (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) u; "swish_clamp": with g' = min(g, limit) and
+    u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1)."""
     n, inter = out.shape
     assert gate_up.shape == (n, 2 * inter)
-    _call("generic", "nncpu_swiglu", _ptr(gate_up), _i(_code(gate_up)), _ptr(out), _i(_code(out)), _i(n),
-          _i(inter), _stream())
+    _call("generic", "nncpu_gated_act", _ptr(gate_up), _i(_code(gate_up)), _ptr(out), _i(_code(out)), _i(n),
+          _i(inter), _i(GATED_ACTS[kind]), _f(limit), _stream())
+
+
+def swiglu(gate_up, out) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    gated_act(gate_up, out, "silu")
+
+
+def stream_add(x, rows=None, vec=None) -> None:
+    """x[t] += rows[t] + vec: float32 x and rows [n, dim], vec [dim] of either element type; either may be None."""
+    n, dim = x.shape
+    assert x.dtype == torch.float32 and (rows is None or (rows.shape == x.shape and rows.dtype == torch.float32))
+    assert vec is None or vec.numel() == dim
+    _call("generic", "nncpu_stream_add", _ptr(x), _ptr(rows), _ptr(vec), _i(_code(vec)), _i(n), _i(dim), _stream())
+
+
+def rmsnorm_dual(x, gamma1, eps1: float, gamma2, eps2: float, out1, out2) -> None:
+    """out1 = rmsnorm(x) * gamma1 and out2 = rmsnorm(x) * gamma2 in one pass over float32 x [n, dim]."""
+    n, dim = x.shape
+    assert x.dtype == torch.float32 and out1.shape == out2.shape == x.shape and out1.dtype == out2.dtype
+    assert gamma1.numel() == gamma2.numel() == dim and gamma1.dtype == gamma2.dtype
+    _call("generic", "nncpu_rmsnorm_dual", _ptr(x), _ptr(gamma1), _ptr(gamma2), _i(_code(gamma1)), _f(eps1), _f(eps2),
+          _ptr(out1), _ptr(out2), _i(_code(out1)), _i(n), _i(dim), _stream())
+
+
+def linear_heads(x, x_col: int, w, out, out_col: int = 0, gate=None, gate_col: int = 0) -> None:
+    """One product per head: out[t, out_col + b * N : ... + N] = x[t, x_col + b * K : ... + K] . w[b]^T for the heads
+    b of w [B, N, K]; x and out are row-major matrices whose rows hold the heads side by side.  With ``gate``
+    (float32 [n, *]) row t of head b is multiplied by sigmoid(gate[t, gate_col + b]).  32-bit on CUDA cores."""
+    B, N, K = w.shape
+    m = x.shape[0]
+    assert out.shape[0] == m and x.shape[1] >= x_col + B * K and out.shape[1] >= out_col + B * N
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape[0] == m)
+    xe, oe = x.element_size(), out.element_size()
+    _call("generic", "nncpu_linear_heads", _vp(x.data_ptr() + x_col * xe) if not (x.is_meta and _dry) else None,
+          _i(_code(x)), _ptr(w), _i(_code(w)),
+          _vp(out.data_ptr() + out_col * oe) if not (out.is_meta and _dry) else None, _i(_code(out)), _i(m), _i(N), _i(K),
+          _i(B), _i(x.shape[1] - x_col), _i(out.shape[1] - out_col), _i(K), _i(N), _ptr(gate),
+          _i(0 if gate is None else gate.shape[1]), _i(gate_col), _stream())
+
+
+def latent_append(proj, col: int, gamma, eps: float, tok_seq, tok_pos, block_table, pages) -> None:
+    """pages[row of token t] = rmsnorm(proj[t, col : col + rank]) * gamma: the one vector per position that latent
+    attention keeps.  proj float32; pages [n_pages, 1, PAGE, rank]."""
+    n = proj.shape[0]
+    rank = pages.shape[-1]
+    assert proj.dtype == torch.float32 and pages.shape[1] == 1 and gamma.numel() == rank
+    _call("generic", "nncpu_latent_append", _ptr(proj), _i(proj.shape[1]), _i(col), _ptr(gamma), _i(_code(gamma)), _f(eps),
+          _ptr(tok_seq), _ptr(tok_pos), _ptr(block_table), _i(block_table.shape[1]), _ptr(pages), _i(_code(pages)),
+          _i(n), _i(rank), _stream())
+
+
+def moe_route(logits, top: int, ids, weights) -> None:
+    """Per row of float32 logits [n, E]: ids [n, top] (int32) of the largest logits in descending order (the lower
+    index wins a tie) and weights [n, top] (float32), the softmax over those logits alone."""
+    n, E = logits.shape
+    assert logits.dtype == torch.float32 and ids.dtype == torch.int32 and weights.dtype == torch.float32
+    assert ids.shape == weights.shape == (n, top)
+    _call("generic", "nncpu_moe_route", _ptr(logits), _i(n), _i(E), _i(top), _ptr(ids), _ptr(weights), _stream())
+
+
+def moe_experts(x, w_gate, w_up, w_down, ids, weights, act, out, kind: str, limit: float = 0.0) -> None:
+    """out[t] += sum_c weights[t, c] * W_down[e] act(W_gate[e] x_t, W_up[e] x_t) with e = ids[t, c].  Weights are
+    [E, ff, width] (gate, up) and [E, width, ff] (down); ``act`` [n * top, ff] is scratch in the run's type; out is the
+    float32 stream.  Every token reads its experts' rows itself: the kernel for few tokens and for every size and type."""
+    n, width = x.shape
+    E, ff, _ = w_gate.shape
+    top = ids.shape[1]
+    assert w_up.shape == (E, ff, width) and w_down.shape == (E, width, ff) and w_gate.dtype == w_up.dtype == w_down.dtype
+    assert act.shape == (n * top, ff) and out.shape == (n, width) and out.dtype == torch.float32
+    _call("generic", "nncpu_moe_experts", _ptr(x), _i(_code(x)), _ptr(w_gate), _ptr(w_up), _ptr(w_down), _i(_code(w_gate)),
+          _ptr(ids), _ptr(weights), _ptr(act), _i(_code(act)), _ptr(out), _i(n), _i(top), _i(width), _i(ff), _i(E),
+          _i(GATED_ACTS[kind]), _f(limit), _stream())
 
 
 def xielu(x, params, out) -> None:

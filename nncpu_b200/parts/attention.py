@@ -11,7 +11,9 @@ An entry that reads another entry's cache has no k/v projection at all
 Options a spec may switch on: value heads of another size than the query/key heads (``v_head_dim``), a
 distance bias per head (``slope_base`` b: head h of H takes 2^(-b (h + 1) / H) * (i - j) off the scaled score
 of query i and key j), and a query temperature (the query at position p times
-1 + coef * ln(floor((p + 1) / every) + 1)).  Scores, bias and softmax are 32-bit.
+1 + coef * ln(floor((p + 1) / every) + 1)).  Scores, bias and softmax are 32-bit.  Which earlier keys a query sees is
+``window`` (the last n up to itself) or ``chunk`` (those of its own block of n positions, blocks counted from position
+0 of the sequence) or neither (all); the kernels know it as one number, ``ops.key_span``.
 """
 from __future__ import annotations
 
@@ -52,11 +54,12 @@ class Attention(Mixer):
         self.unfused = self.plain_core or s.slope_base != 0.0 or s.q_temp_coef != 0.0
         self.q_temp = (s.q_temp_coef, s.q_temp_every) if s.q_temp_coef != 0.0 else None
         self.position = None if s.position is None else base.build("position", s.position)
+        self.span = ops.key_span(s.window, s.chunk)     # what the kernels take as their ``window``
 
     def kv_request(self):
         s = self.spec
         return None if self.shared_kv else KVRequest(s.n_kv_heads, s.head_dim, s.window,
-                                                     0 if self.v_dim == s.head_dim else self.v_dim)
+                                                     0 if self.v_dim == s.head_dim else self.v_dim, chunk=s.chunk)
 
     def _proj_names(self):
         return ["q_proj"] if self.shared_kv else ["q_proj", "k_proj", "v_proj"]
@@ -140,7 +143,7 @@ class Attention(Mixer):
                     ops.attention_decode_mma_from_qkv(qkv, self.q_gamma, self.k_gamma, eps, cos_sin, cache.k_pages,
                                                       cache.v_pages, not self.shared_kv, cache.block_table, ctx.tok_seq,
                                                       ctx.tok_pos, attn, scratch, s.n_heads, s.n_kv_heads, s.head_dim,
-                                                      s.scale, s.window, n_splits, s.slope_base, self.q_temp)
+                                                      s.scale, self.span, n_splits, s.slope_base, self.q_temp)
             else:
                 q = rt.empty(n, self.q_size)
                 with rt.phase("attn_rope"):
@@ -160,7 +163,7 @@ class Attention(Mixer):
         if not perf.enabled():
             return perf._NULL
         s = self.spec
-        keys = ctx.span_sum(s.window)
+        keys = ctx.span_sum(s.window, s.chunk)
         return self.rt.phase("attn_core", nbytes=1.0 * keys * s.n_kv_heads * (s.head_dim + self.v_dim) * cache.k_pages.element_size(),
                              flops=2.0 * keys * (self.q_size + self.out_size))
 
@@ -177,7 +180,8 @@ class Attention(Mixer):
         """Splits of every token's keys in a decode step, and the scratch their merge needs (None: they merge
         inside a thread-block cluster)."""
         s = self.spec
-        longest = min(ctx.max_kv_len, s.window) if s.window > 0 else ctx.max_kv_len
+        limit = s.window or s.chunk
+        longest = min(ctx.max_kv_len, limit) if limit > 0 else ctx.max_kv_len
         n_splits = ops.attention_decode_splits(ctx.n_tokens, s.n_kv_heads, longest, self.rt.sm_count)
         floats = 0 if n_splits <= ops.DECODE_CLUSTER_MAX_SPLITS else ops.attention_decode_scratch_floats(
             ctx.n_tokens, s.n_heads, s.n_kv_heads, s.head_dim, n_splits)
@@ -199,20 +203,20 @@ class Attention(Mixer):
         s = self.spec
         if self.plain_core or not ops.attention_mma_supported(s.n_heads, s.n_kv_heads, s.head_dim, q, cache.k_pages, attn):
             ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos, attn,
-                          s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, self.v_dim, s.slope_base)
+                          s.n_heads, s.n_kv_heads, s.head_dim, s.scale, self.span, self.v_dim, s.slope_base)
         elif ctx.is_decode:
             n_splits, scratch = self._decode_splits(ctx)
             ops.attention_decode_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos,
-                                     attn, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, n_splits,
+                                     attn, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, self.span, n_splits,
                                      s.slope_base)
         elif ctx.n_tokens >= 32 * ctx.n_seqs and ops.attention_prefill_tc_supported(
                 s.n_heads, s.n_kv_heads, s.head_dim, q, cache.k_pages, attn):
             # prompts: 128-row tiles on the tcgen05 tensor cores
             ops.attention_prefill_tc(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.cu_seqlens, ctx.tok_pos,
                                      attn, self.rt.workspace.status, ctx.n_seqs, s.n_heads, s.n_kv_heads, s.head_dim,
-                                     s.scale, s.window, s.slope_base)
+                                     s.scale, self.span, s.slope_base)
         else:
             # a few new tokens per sequence: 64-row tiles
             ops.attention_prefill_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.cu_seqlens, ctx.tok_pos,
-                                      attn, ctx.n_seqs, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window,
+                                      attn, ctx.n_seqs, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, self.span,
                                       s.slope_base)

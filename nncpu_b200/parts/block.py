@@ -1,6 +1,8 @@
 """Arrangements of parts in a layer.  "prenorm":
 x += mixer(norm1(x)); x += feed_forward(norm2(x))
 (crates/nncpu/src/model/forward.rs:735-803 without the Gemma post-norms).
+"sandwich" norms each sublayer's output as well; "parallel" lets both sublayers read the stream as it enters
+the layer: x += mixer(norm1(x)) + feed_forward(norm2(x)).
 The residual stream stays in float32 from the embedding to the final norm.
 """
 from __future__ import annotations
@@ -8,6 +10,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
+from ..weights.params import ParamSpec
 from . import base
 from .base import Block, NormRequest, register_block
 
@@ -170,3 +173,67 @@ class SandwichBlock(Block):
                     else:
                         self._close(ctx, self.norm2_post, branch, residual, None, None)
         ctx.next_norm = after       # the block that follows finds its request there, fulfilled or not
+
+
+@register_block("parallel")
+class ParallelBlock(Block):
+    """Both sublayers read the stream as it enters the layer: x += mixer(norm1(x)) + feed_forward(norm2(x)).
+
+    The two norms are of the same rows, so they run as one kernel that takes the sum of squares once; both outputs are
+    made before the mixer adds into the stream.  A layer without a feed-forward has the mixer alone (a ``norm2``
+    tensor that its file may still hold is accepted and not used).  The sublayers add into the 32-bit stream one
+    after the other."""
+
+    def __init__(self, spec, reads_other_cache: bool = False):
+        kwargs = {"reads_other_cache": True} if reads_other_cache else {}
+        self.norm1 = base.build("norm", spec.norm1)
+        self.mixer = base.build("mixer", spec.mixer, **kwargs)
+        self.feed_forward = None if spec.feed_forward is None else base.build("feed_forward", spec.feed_forward)
+        self.norm2 = None if self.feed_forward is None else base.build("norm", spec.norm2)
+        self._spare = None
+        if self.feed_forward is None:
+            n1 = spec.norm1
+            name = spec.norm2.name + spec.norm2.suffix if spec.norm2 is not None else None
+            if name is None and n1.name.endswith("norm1"):
+                name = n1.name[:-1] + "2" + n1.suffix
+            self._spare = name
+        self._parts = tuple(p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None)
+
+    def params(self):
+        p = [q for part in self._parts for q in part.params()]
+        if self._spare is not None:
+            p.append(ParamSpec(self._spare, (self.norm1.size,), required=False, init=("one_plus_normal", 0.1)))
+        return p
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        for part in self._parts:
+            part.bind(tensors, rt)
+
+    def weight_bytes(self):
+        return sum(part.weight_bytes() for part in self._parts)
+
+    def cache_requests(self):
+        return [(self.mixer.kv_request(), self.mixer.state_request())]
+
+    def _norms(self, ctx, residual):
+        n1, n2, rt = self.norm1, self.norm2, self.rt
+        if n2 is None:
+            return n1.forward(ctx, residual), None
+        if (getattr(n1, "offset", 1.0) == 0.0 and getattr(n2, "offset", 1.0) == 0.0 and n1.size == n2.size
+                and n1.gamma.dtype == n2.gamma.dtype and residual.dtype == torch.float32):
+            x1, x2 = rt.empty(*residual.shape), rt.empty(*residual.shape)
+            with rt.phase("norm"):
+                ops.rmsnorm_dual(residual, n1.gamma, n1.eps, n2.gamma, n2.eps, x1, x2)
+            return x1, x2
+        return n1.forward(ctx, residual), n2.forward(ctx, residual)
+
+    def forward(self, ctx, residual, caches):
+        ctx.next_norm = ctx.after_block = None      # two norms read what this block leaves: they run as a kernel
+        with self.rt.scope():
+            x1, x2 = self._norms(ctx, residual)
+            with self.rt.scope():
+                self.mixer.forward(ctx, x1, residual, caches[0])
+            if self.feed_forward is not None:
+                with self.rt.scope():
+                    self.feed_forward.forward(ctx, x2, residual)

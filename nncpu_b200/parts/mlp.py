@@ -1,7 +1,8 @@
 """Feed-forwards.  Gated: down(act(gate(x)) * up(x)) with act = SiLU
 (crates/nncpu/src/model/forward.rs:763-782,
-crates/nncpu/src/kernels/scalar.rs:146-150).  gate and up are stored as one
+crates/nncpu/src/kernels/scalar.rs:146-150) or one of the other gated activations.  gate and up are stored as one
 matrix so the input is read once; the result is added to the residual stream.
+Routed experts: a router picks a few small gated feed-forwards per token.
 Dense: down(act(up(x) + b_up)) + b_down with act = xIELU, an activation with two learned numbers.
 """
 from __future__ import annotations
@@ -13,27 +14,41 @@ import torch
 from ..errors import UnsupportedModel
 from ..kernels import ops
 from ..weights.params import ParamSpec
-from .base import FeedForward, register_feed_forward
+from .base import DeferredNorm, FeedForward, register_feed_forward
+
+
+GATED_ACTIVATIONS = ("silu", "gelu_tanh", "swish_clamp")
 
 
 @register_feed_forward("gated_mlp")
 class GatedMlp(FeedForward):
+    """down(act(gate(x), up(x))) with act one of ``GATED_ACTIVATIONS`` (see ``ops.gated_act``), computed in 32-bit on
+    the two products' 32-bit results: in the gate/up product's epilogue on the tensor cores, in a kernel of its own
+    elsewhere."""
     accepts_deferred_norm = True    # x goes to Runtime.linear, which finishes a norm's unfinished output
 
     def __init__(self, spec):
-        if spec.activation != "silu":
-            raise UnsupportedModel(f"{spec.name}: activation {spec.activation!r} is not supported (supported: silu)")
+        if spec.activation not in GATED_ACTIVATIONS:
+            raise UnsupportedModel(f"{spec.name}: activation {spec.activation!r} is not supported "
+                                   f"(supported: {', '.join(GATED_ACTIVATIONS)})")
+        if spec.tensor_names not in ("proj", "short"):
+            raise UnsupportedModel(f"{spec.name}: tensor names of style {spec.tensor_names!r}")
         self.spec = spec
+        self.activation = None if spec.activation == "silu" else (spec.activation, float(spec.limit), 0.0)
+
+    def _tensor(self, which: str) -> str:
+        s = self.spec
+        return f"{s.name}.{which}" if s.tensor_names == "short" else f"{s.name}.{which}_proj.weight"
 
     def params(self):
         s = self.spec
-        return [ParamSpec(f"{s.name}.gate_proj.weight", (s.intermediate_size, s.hidden_size)),
-                ParamSpec(f"{s.name}.up_proj.weight", (s.intermediate_size, s.hidden_size)),
-                ParamSpec(f"{s.name}.down_proj.weight", (s.hidden_size, s.intermediate_size))]
+        return [ParamSpec(self._tensor("gate"), (s.intermediate_size, s.hidden_size)),
+                ParamSpec(self._tensor("up"), (s.intermediate_size, s.hidden_size)),
+                ParamSpec(self._tensor("down"), (s.hidden_size, s.intermediate_size))]
 
     def bind(self, tensors, rt):
         s, self.rt = self.spec, rt
-        gate, up = tensors.pop(f"{s.name}.gate_proj.weight"), tensors.pop(f"{s.name}.up_proj.weight")
+        gate, up = tensors.pop(self._tensor("gate")), tensors.pop(self._tensor("up"))
         # On the tensor-core path the activation runs in the product's epilogue, on the 32-bit
         # accumulators; for that, gate and up rows are interleaved in blocks of 8.
         self.fused = (gate.dtype == up.dtype and s.intermediate_size % 8 == 0
@@ -44,7 +59,7 @@ class GatedMlp(FeedForward):
         else:
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         del gate, up
-        self.w_down = tensors[f"{s.name}.down_proj.weight"]
+        self.w_down = tensors[self._tensor("down")]
 
     def weight_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
@@ -55,16 +70,83 @@ class GatedMlp(FeedForward):
         act = rt.empty(n, s.intermediate_size)
         if self.fused:
             with rt.phase("ffn_gate_up", self.w_gate_up, n):
-                rt.linear(x, self.w_gate_up, None, act, epilogue="swiglu")
+                rt.linear(x, self.w_gate_up, None, act, epilogue="swiglu", activation=self.activation)
         else:
-            gate_up = rt.empty(n, 2 * s.intermediate_size)
+            gate_up = rt.empty(n, 2 * s.intermediate_size, dtype=torch.float32)
             with rt.phase("ffn_gate_up", self.w_gate_up, n):
                 rt.linear(x, self.w_gate_up, None, gate_up)
             with rt.phase("ffn_act"):
-                ops.swiglu(gate_up, act)
+                ops.gated_act(gate_up, act, s.activation, s.limit)
         with rt.phase("ffn_down", self.w_down, n):
             # the last write into the residual stream: it may leave the next norm its input
-            rt.linear(act, self.w_down, None, residual, accumulate=True, then_norm=getattr(ctx, "next_norm", None))
+            rt.linear(act, self.w_down, None, residual, accumulate=not getattr(ctx, "branch_is_fresh", False),
+                      then_norm=getattr(ctx, "next_norm", None))
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    """Every token runs the ``top`` of ``n_experts`` gated feed-forwards with the largest router logits, weighted by
+    the softmax over those logits alone, and (optionally) a shared gated feed-forward.
+
+    The router is a 32-bit product (its input may be the run's rounding of the norm's output) with a bias; the choice
+    and the weights are made on the device by one kernel, so a step never waits for the host.  Experts' matrices are
+    stacked [n_experts, rows, cols] when the weights are bound."""
+
+    def __init__(self, spec):
+        if spec.activation not in GATED_ACTIVATIONS:
+            raise UnsupportedModel(f"{spec.name}: activation {spec.activation!r} is not supported")
+        if not 0 < spec.top <= spec.n_experts:
+            raise UnsupportedModel(f"{spec.name}: the top {spec.top} of {spec.n_experts} experts")
+        self.spec = spec
+        self.shared = None if spec.shared is None else GatedMlp(spec.shared)
+
+    def params(self):
+        s, p = self.spec, []
+        for e in range(s.n_experts):
+            p += [ParamSpec(f"{s.name}.e{e}.gate", (s.intermediate_size, s.hidden_size)),
+                  ParamSpec(f"{s.name}.e{e}.up", (s.intermediate_size, s.hidden_size)),
+                  ParamSpec(f"{s.name}.e{e}.down", (s.hidden_size, s.intermediate_size))]
+        p += [ParamSpec(f"{s.name}.router", (s.n_experts, s.hidden_size), init=("normal", 0.5)),
+              ParamSpec(f"{s.name}.router.b", (s.n_experts,), init=("normal", 0.5))]
+        return p + (self.shared.params() if self.shared is not None else [])
+
+    def bind(self, tensors, rt):
+        s, self.rt = self.spec, rt
+        def stack(which):
+            parts = [tensors.pop(f"{s.name}.e{e}.{which}") for e in range(s.n_experts)]
+            return torch.stack(parts, dim=0).contiguous()
+        self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+        self.w_router, self.b_router = tensors[f"{s.name}.router"], tensors[f"{s.name}.router.b"]
+        if self.shared is not None:
+            self.shared.bind(tensors, rt)
+
+    def weight_bytes(self):
+        """Bytes a decode step of one token reads: the router, the chosen experts, the shared expert."""
+        s = self.spec
+        per_expert = 3 * s.intermediate_size * s.hidden_size * self.w_gate.element_size()
+        return (self.w_router.numel() * self.w_router.element_size() + s.top * per_expert
+                + (self.shared.weight_bytes() if self.shared is not None else 0))
+
+    def forward(self, ctx, x, residual):
+        s, rt = self.spec, self.rt
+        if isinstance(x, DeferredNorm):
+            x = x.finish(ctx)
+        n = x.shape[0]
+        if getattr(ctx, "branch_is_fresh", False):
+            raise UnsupportedModel(f"{s.name}: routed experts add into the stream they are given")
+        logits = rt.empty(n, s.n_experts, dtype=torch.float32)
+        ids = rt.empty(n, s.top, dtype=torch.int32)
+        weights = rt.empty(n, s.top, dtype=torch.float32)
+        with rt.phase("moe_route", self.w_router, n):
+            ops.linear_simt(x, self.w_router, self.b_router, logits)
+            ops.moe_route(logits, s.top, ids, weights)
+        act = rt.empty(n * s.top, s.intermediate_size)
+        per_expert = 3.0 * s.intermediate_size * s.hidden_size
+        with rt.phase("moe_experts", nbytes=min(n * s.top, s.n_experts) * per_expert * self.w_gate.element_size(),
+                      flops=2.0 * n * s.top * per_expert):
+            ops.moe_experts(x, self.w_gate, self.w_up, self.w_down, ids, weights, act, residual, s.activation, s.limit)
+        if self.shared is not None:
+            self.shared.forward(ctx, x, residual)
 
 
 @register_feed_forward("dense_mlp")
