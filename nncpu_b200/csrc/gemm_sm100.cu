@@ -392,6 +392,170 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 }
 
 // ---------------------------------------------------------------------------
+// Grouped product: the rows of A come in groups that follow one another (tokens sorted by the expert they were
+// routed to), and group e is multiplied with its own matrix, rows e * N .. e * N + N - 1 of B.  C[r, :] =
+// A[r, :] . B_e^T for the rows r of group e, with the plain or the gated epilogue.  Which 128-row tiles there are
+// is decided on the device by the kernel that sorted the rows (a plan: the tiles' groups, first rows and their
+// groups' ends, and how many tiles there are), so the host never waits for the router.  A tile that reaches beyond
+// its group's end multiplies rows of the next group, or rows beyond A (zeros), too; those rows are not stored.
+// Otherwise this is gemm_bf16_kernel: persistent blocks, work item w = (tile w % tiles, columns w / tiles), a ring
+// of TMA stages, two accumulators in tensor memory, every wait bounded.
+// ---------------------------------------------------------------------------
+struct GroupPlan {
+    const int* n_tiles;       // [1] 128-row tiles over all groups
+    const int* tile_group;    // [max tiles] the group of each tile
+    const int* tile_row0;     // [max tiles] its first row of A (and of C)
+    const int* tile_row_end;  // [max tiles] the end of its group's rows
+    int max_tiles;
+};
+
+template <int BN, int kStages, int kEpi>
+__global__ void __launch_bounds__(kThreads)
+gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmParams p, const GroupPlan g) {
+    constexpr int kBytesA = kBlockM * kBlockK * 2;
+    constexpr int kBytesB = BN * kBlockK * 2;
+    constexpr int kAccCols = BN < 32 ? 32 : BN;
+    constexpr int kTmemCols = 2 * kAccCols;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + kStages * kBytesA;
+    uint64_t* full = (uint64_t*)(smem_b + kStages * kBytesB);
+    uint64_t* empty = full + kStages;
+    uint64_t* acc_full = empty + kStages;   // [2]
+    uint64_t* acc_empty = acc_full + 2;     // [2]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_a = min(*g.n_tiles, g.max_tiles);
+    const int n_tiles = tiles_a * p.tiles_b;
+    const unsigned long long limit = p.wait_ns ? p.wait_ns : kWaitLimitNs;
+    const int my_tiles = (int)blockIdx.x < n_tiles ? (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int my_runs = my_tiles * p.kb_total;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            for (int r = 0; r < my_runs; ++r) {
+                const int w = blockIdx.x + (r / p.kb_total) * gridDim.x, kb = r % p.kb_total;
+                const int ta = w % tiles_a;
+                const int m0 = g.tile_row0[ta], n0 = g.tile_group[ta] * p.rows_b + (w / tiles_a) * BN;
+                const int s = r % kStages;
+                if (r >= kStages && !mbar_wait(&empty[s], ((r / kStages) & 1) ^ 1, limit)) {
+                    atomicExch(p.status, kTimeoutEmpty);
+                    ok = false;
+                    break;
+                }
+                mbar_expect_tx(&full[s], kBytesA + kBytesB);
+                tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], kb * kBlockK, m0);
+                tma_load_2d(smem_b + s * kBytesB, &map_b, &full[s], kb * kBlockK, n0);
+                issued = r + 1;
+            }
+            if (!ok) {
+                // let the copies already in flight land before the block gives up its shared memory
+                for (int r = max(0, issued - kStages); r < issued; ++r) mbar_wait(&full[r % kStages], (r / kStages) & 1, limit);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc_bf16(kBlockM, BN);
+            int kb_run = 0, it = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < n_tiles && ok; w += gridDim.x, ++it) {
+                const int buf = it & 1;
+                if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1, limit)) {
+                    atomicExch(p.status, kTimeoutAccumEmpty);
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kAccCols);
+                for (int kb = 0; kb < p.kb_total; ++kb, ++kb_run) {
+                    const int s = kb_run % kStages;
+                    if (!mbar_wait(&full[s], (kb_run / kStages) & 1, limit)) {
+                        atomicExch(p.status, kTimeoutFull);
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(smem_a + s * kBytesA);
+                    const uint32_t b_addr = smem_u32(smem_b + s * kBytesB);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                        const uint64_t a_desc = smem_desc_sw128(a_addr + k * kUmmaK * 2);
+                        const uint64_t b_desc = smem_desc_sw128(b_addr + k * kUmmaK * 2);
+                        umma_bf16(tmem_d, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty[s]);
+                }
+                if (ok) umma_commit(&acc_full[buf]);
+            }
+        }
+    } else {
+        // Epilogue: warp w may read the tensor-memory lanes 32 * (w % 4) .. + 31.
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        GemmParams q = p;                 // rows_a becomes the end of the tile's group: rows beyond it are not stored
+        int it = 0;
+        for (int w = blockIdx.x; w < n_tiles; w += gridDim.x, ++it) {
+            const int ta = w % tiles_a;
+            const int a_row = g.tile_row0[ta] + row_in_tile, n0 = (w / tiles_a) * BN;
+            q.rows_a = g.tile_row_end[ta];
+            const int buf = it & 1;
+            if (!mbar_wait(&acc_full[buf], (it >> 1) & 1, limit)) {
+                if (lane == 0) atomicExch(p.status, kTimeoutAccumFull);
+                break;
+            }
+            __syncwarp();
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kAccCols);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                tmem_ld16(taddr + (uint32_t)c0, v);
+                store16<kEpi>(q, a_row, n0 + c0, v);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
 // The same product with the work cut evenly instead of tile by tile ("stream-K"):
 // the units are (output tile, k-block) pairs in tile order, and block c of G
 // takes the units [c U / G, (c + 1) U / G).  Every block therefore streams the
@@ -1642,6 +1806,59 @@ extern "C" int nncpu_linear_tc_wait_probe(const void* X, const void* W, float* o
 // k-blocks dealt out evenly over the SMs; 17 to 64 tokens a cluster per output tile); kPlanEvenFrom17: dealt out
 // evenly from 17 tokens on; kPlanNeverEven: never dealt out evenly; kPlanNoPairs: one SM per 128 x 256 tile;
 // kPlanNarrowUnits: units of 128 weight rows where 256 would be taken.
+template <int kEpi>
+int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, const GroupPlan& g, cudaStream_t stream) {
+    constexpr int BN = 128, kStages = 6;
+    constexpr size_t smem = smem_bytes<BN, kStages>();
+    static bool configured[64] = {};
+    if (first_use_on_this_device(configured)) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_grouped_kernel<BN, kStages, kEpi>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        NN_CHECK(e == cudaSuccess, "gemm (grouped): cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    }
+    const long most = (long)g.max_tiles * p.tiles_b;
+    const int grid = most < sm_count() ? (int)most : sm_count();
+    gemm_grouped_kernel<BN, kStages, kEpi><<<grid, kThreads, smem, stream>>>(ma, mb, p, g);
+    const cudaError_t e = cudaGetLastError();
+    NN_CHECK(e == cudaSuccess, "gemm (grouped): launch failed: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+// C[r, :] = X[r, :] . W_e^T for the rows r of group e (see gemm_grouped_kernel).  X [S, K] bfloat16 holds the groups'
+// rows one group after the other, W [n_groups * N, K] the groups' matrices, C [S, ldc].  Epilogue 0: C has N columns;
+// 1: every matrix holds gate and up rows interleaved in blocks of 8 and C [S, N / 2] receives act(gate) * up, act by
+// `act` as in nncpu_linear_tc.  The plan lies on the device; max_tiles is the most tiles it can name.
+extern "C" int nncpu_linear_tc_grouped(const void* X, const void* W, void* C, int c_dt, int S, int N, int K, int n_groups,
+                                       int lda, int ldc, int epilogue, int act, float act_a, const int* n_tiles,
+                                       const int* tile_group, const int* tile_row0, const int* tile_row_end,
+                                       int max_tiles, int* status, void* stream) {
+    NN_CHECK(S > 0 && N > 0 && K > 0 && n_groups > 0 && max_tiles > 0 && (long)n_groups * N < (1l << 31),
+             "gemm (grouped): %d rows, %d groups of %d x %d", S, n_groups, N, K);
+    NN_CHECK(K % 8 == 0 && lda % 8 == 0 && lda >= K, "gemm (grouped): K %d and lda %d must be multiples of 8", K, lda);
+    NN_CHECK(((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0, "gemm (grouped): operands must be 16-byte aligned");
+    NN_CHECK(epilogue == kPlain || epilogue == kSwiglu, "gemm (grouped): unknown epilogue %d", epilogue);
+    const int n_out = epilogue == kSwiglu ? N / 2 : N;
+    NN_CHECK(ldc >= n_out && (epilogue == kPlain || N % 16 == 0), "gemm (grouped): ldc %d, N %d", ldc, N);
+    NN_CHECK(epilogue == kSwiglu ? (act == kActNone || act == kActGateGelu || act == kActGateSwishClamp) : act == kActNone,
+             "gemm (grouped): activation %d with epilogue %d", act, epilogue);
+    GemmParams p{};
+    p.K = K;
+    p.kb_total = (K + kBlockK - 1) / kBlockK;
+    p.out = C; p.out_dt = c_dt; p.ldc = ldc; p.status = status;
+    const int esize = c_dt == DT_F32 ? 4 : 2;
+    p.vec = ((uintptr_t)C % 16 == 0) && ((size_t)ldc * esize % 16 == 0);
+    p.swap = 0;
+    p.rows_a = S; p.rows_b = N;
+    p.tiles_b = (N + 127) / 128;
+    p.nf.act = act; p.nf.act_a = act_a;
+    CUtensorMap ma, mb;
+    if (int e = g_maps.get(&ma, X, S, K, lda, kBlockM)) return e;
+    if (int e = g_maps.get(&mb, W, n_groups * N, K, K, 128)) return e;
+    GroupPlan g{n_tiles, tile_group, tile_row0, tile_row_end, max_tiles};
+    return epilogue == kSwiglu ? launch_grouped<kSwiglu>(ma, mb, p, g, (cudaStream_t)stream)
+                               : launch_grouped<kPlain>(ma, mb, p, g, (cudaStream_t)stream);
+}
+
 enum Plan : int { kPlanEvenFrom17 = 1, kPlanNeverEven = 2, kPlanNoPairs = 4, kPlanNarrowUnits = 8 };
 
 //

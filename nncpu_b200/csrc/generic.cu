@@ -1803,6 +1803,8 @@ __global__ void __launch_bounds__(kMoeWarps * 32)
 moe_gate_up_kernel(const void* __restrict__ x, int x_dt, const void* __restrict__ wg, const void* __restrict__ wu,
                    int w_dt, const int* __restrict__ ids, void* __restrict__ act, int act_dt, int top, int width, int ff,
                    int n_experts, int kind, float limit) {
+    // wu null: wg holds [n_experts, 2 ff, width] with an expert's gate and up rows interleaved in blocks of 8 (the
+    // layout of the tensor-core products' gated epilogue): gate row j is row 16 (j / 8) + j % 8, up row j eight below
     extern __shared__ float smem[];          // the token's input as floats
     const int s = blockIdx.x, t = s / top;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1810,10 +1812,13 @@ moe_gate_up_kernel(const void* __restrict__ x, int x_dt, const void* __restrict_
     for (int i = threadIdx.x; i < width; i += blockDim.x) smem[i] = ld_f(x, (size_t)t * width + i, x_dt);
     __syncthreads();
     if (e < 0 || e >= n_experts) return;
-    const size_t w0 = (size_t)e * ff * width;
+    const bool mixed = wu == nullptr;
+    const size_t w0 = (size_t)e * ff * width * (mixed ? 2 : 1);
     for (int j = blockIdx.y * kMoeWarps + warp; j < ff; j += gridDim.y * kMoeWarps) {
-        const float g = warp_dot(wg, w0 + (size_t)j * width, w_dt, smem, width, lane);
-        const float u = warp_dot(wu, w0 + (size_t)j * width, w_dt, smem, width, lane);
+        const size_t row = mixed ? (size_t)(((j >> 3) << 4) + (j & 7)) : (size_t)j;
+        const float g = warp_dot(wg, w0 + row * width, w_dt, smem, width, lane);
+        const float u = mixed ? warp_dot(wg, w0 + (row + 8) * width, w_dt, smem, width, lane)
+                              : warp_dot(wu, w0 + row * width, w_dt, smem, width, lane);
         if (lane == 0) st_f(act, (size_t)s * ff + j, act_dt, gated_act_f(g, u, kind, limit));
     }
 }
@@ -1845,6 +1850,7 @@ extern "C" int nncpu_moe_experts(const void* x, int x_dt, const void* wg, const 
     NN_CHECK(n_tok >= 0 && top > 0 && width > 0 && ff > 0 && n_experts > 0, "experts: %d tokens, top %d, %d x %d, %d experts",
              n_tok, top, width, ff, n_experts);
     NN_CHECK(kind >= kGateSilu && kind <= kGateSwishClamp, "experts: activation kind %d", kind);
+    NN_CHECK(wu != nullptr || ff % 8 == 0, "experts: interleaved gate and up rows need a multiple of 8 of them (%d)", ff);
     NN_CHECK((size_t)width * 4 <= 48 * 1024 && (size_t)top * ff * 4 <= 48 * 1024,
              "experts: a token's %d inputs or %d x %d activations do not fit the shared memory of this kernel", width, top, ff);
     if (n_tok == 0) return 0;
@@ -1859,5 +1865,110 @@ extern "C" int nncpu_moe_experts(const void* x, int x_dt, const void* wg, const 
     moe_down_kernel<<<dim3(n_tok, split_down), kMoeWarps * 32, (size_t)top * ff * 4, (cudaStream_t)stream>>>(
         act, act_dt, wd, w_dt, ids, weights, out, top, width, ff, n_experts);
     NN_LAUNCH_OK("experts (down)");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Routed experts for many tokens: the token slots (token, choice) are sorted by expert, the experts' products run
+// as one grouped product on the tensor cores (gemm_sm100.cu), and the choices of a token are added up afterwards.
+//   plan: counts the slots of every expert, gives every slot a row (its expert's rows follow one another; the order
+//     inside an expert is whatever the atomics give, which changes no result: a row's product does not depend on its
+//     place), and lists the 128-row tiles of the grouped product.  One block.
+//   gather: xs[row] = x[slot_of_row[row] / top].
+//   combine: out[t] += sum_c weight[t, c] * y[row_of_slot[t * top + c]], choices in their order.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ ids, int n_slots, int n_experts, int* __restrict__ row_of_slot,
+                int* __restrict__ slot_of_row, int* __restrict__ n_tiles, int* __restrict__ tile_group,
+                int* __restrict__ tile_row0, int* __restrict__ tile_row_end, int max_tiles) {
+    extern __shared__ int plan_smem[];
+    int* count = plan_smem;
+    int* offset = plan_smem + n_experts;
+    int* cursor = plan_smem + 2 * n_experts;
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = cursor[e] = 0;
+    __syncthreads();
+    for (int s = threadIdx.x; s < n_slots; s += blockDim.x) {
+        const int e = ids[s];
+        if (e >= 0 && e < n_experts) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0, tiles = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            offset[e] = acc;
+            for (int r = 0; r < count[e]; r += 128, ++tiles) {
+                if (tiles < max_tiles) {
+                    tile_group[tiles] = e;
+                    tile_row0[tiles] = acc + r;
+                    tile_row_end[tiles] = acc + count[e];
+                }
+            }
+            acc += count[e];
+        }
+        *n_tiles = tiles < max_tiles ? tiles : max_tiles;
+    }
+    __syncthreads();
+    for (int s = threadIdx.x; s < n_slots; s += blockDim.x) {
+        const int e = ids[s];
+        if (e < 0 || e >= n_experts) { row_of_slot[s] = -1; continue; }
+        const int row = offset[e] + atomicAdd(&cursor[e], 1);
+        row_of_slot[s] = row;
+        slot_of_row[row] = s;
+    }
+}
+
+extern "C" int nncpu_moe_plan(const int* ids, int n_slots, int n_experts, int* row_of_slot, int* slot_of_row,
+                              int* n_tiles, int* tile_group, int* tile_row0, int* tile_row_end, int max_tiles,
+                              void* stream) {
+    NN_CHECK(n_slots > 0 && n_experts > 0 && n_experts <= kRouteMaxExperts && max_tiles >= (n_slots + 127) / 128 + n_experts,
+             "experts (plan): %d slots, %d experts, room for %d tiles", n_slots, n_experts, max_tiles);
+    moe_plan_kernel<<<1, 1024, (size_t)3 * n_experts * sizeof(int), (cudaStream_t)stream>>>(
+        ids, n_slots, n_experts, row_of_slot, slot_of_row, n_tiles, tile_group, tile_row0, tile_row_end, max_tiles);
+    NN_LAUNCH_OK("experts (plan)");
+    return 0;
+}
+
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const void* __restrict__ x, int x_dt, const int* __restrict__ slot_of_row, int top,
+                  __nv_bfloat16* __restrict__ xs, int width) {
+    const int row = blockIdx.x;
+    const int t = slot_of_row[row] / top;
+    if (x_dt == DT_BF16 && (width & 7) == 0) {
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + (size_t)t * width);
+        uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)row * width);
+        for (int i = threadIdx.x; i < (width >> 3); i += blockDim.x) dst[i] = src[i];
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x)
+            xs[(size_t)row * width + i] = __float2bfloat16_rn(ld_f(x, (size_t)t * width + i, x_dt));
+    }
+}
+
+extern "C" int nncpu_moe_gather(const void* x, int x_dt, const int* slot_of_row, int top, void* xs, int n_slots,
+                                int width, void* stream) {
+    NN_CHECK(n_slots > 0 && top > 0 && width > 0, "experts (gather): %d slots of %d", n_slots, width);
+    moe_gather_kernel<<<n_slots, 256, 0, (cudaStream_t)stream>>>(x, x_dt, slot_of_row, top, (__nv_bfloat16*)xs, width);
+    NN_LAUNCH_OK("experts (gather)");
+    return 0;
+}
+
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const void* __restrict__ y, int y_dt, const int* __restrict__ row_of_slot,
+                   const float* __restrict__ weights, float* __restrict__ out, int top, int width) {
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float sum = 0.0f;
+        for (int c = 0; c < top; ++c) {
+            const int row = row_of_slot[(size_t)t * top + c];
+            if (row >= 0) sum = fmaf(weights[(size_t)t * top + c], ld_f(y, (size_t)row * width + i, y_dt), sum);
+        }
+        out[(size_t)t * width + i] += sum;
+    }
+}
+
+extern "C" int nncpu_moe_combine(const void* y, int y_dt, const int* row_of_slot, const float* weights, float* out,
+                                 int n_tok, int top, int width, void* stream) {
+    NN_CHECK(n_tok > 0 && top > 0 && width > 0, "experts (combine): %d tokens of %d", n_tok, width);
+    moe_combine_kernel<<<n_tok, 256, 0, (cudaStream_t)stream>>>(y, y_dt, row_of_slot, weights, out, top, width);
+    NN_LAUNCH_OK("experts (combine)");
     return 0;
 }

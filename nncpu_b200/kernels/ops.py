@@ -542,12 +542,13 @@ def linear_heads(x, x_col: int, w, out, out_col: int = 0, gate=None, gate_col: i
     B, N, K = w.shape
     m = x.shape[0]
     assert out.shape[0] == m and x.shape[1] >= x_col + B * K and out.shape[1] >= out_col + B * N
-    assert gate is None or (gate.dtype == torch.float32 and gate.shape[0] == m)
+    assert x.is_contiguous() and out.is_contiguous()
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape[0] == m and gate.is_contiguous())
     xe, oe = x.element_size(), out.element_size()
     _call("generic", "nncpu_linear_heads", _vp(x.data_ptr() + x_col * xe) if not (x.is_meta and _dry) else None,
           _i(_code(x)), _ptr(w), _i(_code(w)),
           _vp(out.data_ptr() + out_col * oe) if not (out.is_meta and _dry) else None, _i(_code(out)), _i(m), _i(N), _i(K),
-          _i(B), _i(x.shape[1] - x_col), _i(out.shape[1] - out_col), _i(K), _i(N), _ptr(gate),
+          _i(B), _i(x.shape[1]), _i(out.shape[1]), _i(K), _i(N), _ptr(gate),
           _i(0 if gate is None else gate.shape[1]), _i(gate_col), _stream())
 
 
@@ -573,16 +574,72 @@ def moe_route(logits, top: int, ids, weights) -> None:
 
 def moe_experts(x, w_gate, w_up, w_down, ids, weights, act, out, kind: str, limit: float = 0.0) -> None:
     """out[t] += sum_c weights[t, c] * W_down[e] act(W_gate[e] x_t, W_up[e] x_t) with e = ids[t, c].  Weights are
-    [E, ff, width] (gate, up) and [E, width, ff] (down); ``act`` [n * top, ff] is scratch in the run's type; out is the
-    float32 stream.  Every token reads its experts' rows itself: the kernel for few tokens and for every size and type."""
+    [E, ff, width] (gate, up) and [E, width, ff] (down); with ``w_up`` None, ``w_gate`` is [E, 2 ff, width] with an
+    expert's gate and up rows interleaved in blocks of 8 (the layout of the grouped product).  ``act`` [n * top, ff] is
+    scratch in the run's type; out is the float32 stream.  Every token reads its experts' rows itself: the kernel for
+    few tokens and for every size and type."""
     n, width = x.shape
-    E, ff, _ = w_gate.shape
+    E, ff = w_down.shape[0], w_down.shape[2]
     top = ids.shape[1]
-    assert w_up.shape == (E, ff, width) and w_down.shape == (E, width, ff) and w_gate.dtype == w_up.dtype == w_down.dtype
+    assert w_down.shape == (E, width, ff) and w_gate.dtype == w_down.dtype
+    assert w_gate.shape == ((E, 2 * ff, width) if w_up is None else (E, ff, width))
+    assert w_up is None or (w_up.shape == (E, ff, width) and w_up.dtype == w_gate.dtype)
     assert act.shape == (n * top, ff) and out.shape == (n, width) and out.dtype == torch.float32
     _call("generic", "nncpu_moe_experts", _ptr(x), _i(_code(x)), _ptr(w_gate), _ptr(w_up), _ptr(w_down), _i(_code(w_gate)),
           _ptr(ids), _ptr(weights), _ptr(act), _i(_code(act)), _ptr(out), _i(n), _i(top), _i(width), _i(ff), _i(E),
           _i(GATED_ACTS[kind]), _f(limit), _stream())
+
+
+def moe_plan_tiles(n_slots: int, n_experts: int) -> int:
+    """The most 128-row tiles a grouped product over ``n_slots`` rows in ``n_experts`` groups can have."""
+    return (n_slots + 127) // 128 + n_experts
+
+
+def moe_plan(ids, n_experts: int, row_of_slot, slot_of_row, plan) -> None:
+    """Sorts the token slots (row-major ``ids`` [n, top]) by expert: ``row_of_slot`` / ``slot_of_row`` (int32 [n * top])
+    map slots to rows and back, and ``plan`` (int32 [1 + 3 * moe_plan_tiles]) receives the number of 128-row tiles and
+    per tile its expert, first row and its expert's last row + 1, for ``linear_tc_grouped``."""
+    S = ids.numel()
+    mt = moe_plan_tiles(S, n_experts)
+    assert ids.dtype == row_of_slot.dtype == slot_of_row.dtype == plan.dtype == torch.int32
+    assert row_of_slot.numel() == slot_of_row.numel() == S and plan.numel() == 1 + 3 * mt and plan.is_contiguous()
+    base, dry = (0 if plan.is_meta else plan.data_ptr()), plan.is_meta and _dry
+    at = lambda k: None if dry else _vp(base + 4 * k)
+    _call("generic", "nncpu_moe_plan", _ptr(ids), _i(S), _i(n_experts), _ptr(row_of_slot), _ptr(slot_of_row), at(0), at(1),
+          at(1 + mt), at(1 + 2 * mt), _i(mt), _stream())
+
+
+def moe_gather(x, slot_of_row, top: int, xs) -> None:
+    """xs[row] = x[slot_of_row[row] // top] as bfloat16: the tokens' rows in the order of the grouped product."""
+    S, width = xs.shape
+    assert xs.dtype == torch.bfloat16 and x.shape[1] == width and slot_of_row.numel() == S
+    _call("generic", "nncpu_moe_gather", _ptr(x), _i(_code(x)), _ptr(slot_of_row), _i(top), _ptr(xs), _i(S), _i(width), _stream())
+
+
+def moe_combine(y, row_of_slot, weights, out) -> None:
+    """out[t] += sum_c weights[t, c] * y[row_of_slot[t * top + c]], choices in their order; out float32."""
+    n, top = weights.shape
+    assert out.dtype == torch.float32 and out.shape == (n, y.shape[1]) and row_of_slot.numel() == n * top
+    _call("generic", "nncpu_moe_combine", _ptr(y), _i(_code(y)), _ptr(row_of_slot), _ptr(weights), _ptr(out), _i(n), _i(top),
+          _i(out.shape[1]), _stream())
+
+
+def linear_tc_grouped(xs, w, out, plan, n_experts: int, workspace: GemmWorkspace, epilogue: str = "plain",
+                      activation=None) -> None:
+    """out[r] = xs[r] . w[e]^T for the rows r of expert e, on the tcgen05 tensor cores; xs [S, K] bfloat16 sorted by
+    expert (``moe_plan``), w [E, N, K] bfloat16.  With ``epilogue="swiglu"`` every expert's rows are gate and up rows
+    interleaved in blocks of 8 and out [S, N / 2] receives act(gate) * up (``activation`` as in ``linear_tc``)."""
+    S, K = xs.shape
+    E, N, _ = w.shape
+    mt = moe_plan_tiles(S, n_experts)
+    assert E == n_experts and w.shape[2] == K and xs.dtype == w.dtype == torch.bfloat16 and w.is_contiguous()
+    assert out.shape == (S, N // 2 if epilogue == "swiglu" else N) and plan.numel() == 1 + 3 * mt
+    base, dry = (0 if plan.is_meta else plan.data_ptr()), plan.is_meta and _dry
+    at = lambda k: None if dry else _vp(base + 4 * k)
+    act, a, _b = _activation(activation)
+    _call("gemm_sm100", "nncpu_linear_tc_grouped", _ptr(xs), _ptr(w), _ptr(out), _i(_code(out)), _i(S), _i(N), _i(K), _i(E),
+          _i(K), _i(out.shape[1]), _i(EPILOGUES[epilogue]), act, a, at(0), at(1), at(1 + mt), at(1 + 2 * mt), _i(mt),
+          _ptr(workspace.status), _stream())
 
 
 def xielu(x, params, out) -> None:

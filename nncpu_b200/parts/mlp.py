@@ -18,6 +18,9 @@ from .base import DeferredNorm, FeedForward, register_feed_forward
 
 
 GATED_ACTIVATIONS = ("silu", "gelu_tanh", "swish_clamp")
+# With more token slots (token, choice) than this per expert, the experts run as one grouped product on the tensor
+# cores; below it every slot reads its expert's rows itself.
+GROUPED_FROM_SLOTS_PER_EXPERT = 1
 
 
 @register_feed_forward("gated_mlp")
@@ -115,7 +118,19 @@ class RoutedExperts(FeedForward):
         def stack(which):
             parts = [tensors.pop(f"{s.name}.e{e}.{which}") for e in range(s.n_experts)]
             return torch.stack(parts, dim=0).contiguous()
-        self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+        gate, up, self.w_down = stack("gate"), stack("up"), stack("down")
+        # Where the tensor cores take the sizes, an expert's gate and up rows are interleaved in blocks of 8, so that
+        # the grouped product applies the activation in its epilogue; the kernel for few tokens reads the same layout.
+        h, f = s.hidden_size, s.intermediate_size
+        self.grouped = (gate.dtype == up.dtype == self.w_down.dtype and f % 8 == 0
+                        and rt.tensor_cores_take(rt.dtype, gate[0], h) and rt.tensor_cores_take(rt.dtype, self.w_down[0], f))
+        if self.grouped:
+            self.w_gate = torch.stack([gate.view(s.n_experts, -1, 8, h), up.view(s.n_experts, -1, 8, h)],
+                                      dim=2).reshape(s.n_experts, 2 * f, h).contiguous()
+            self.w_up = None
+        else:
+            self.w_gate, self.w_up = gate, up
+        del gate, up
         self.w_router, self.b_router = tensors[f"{s.name}.router"], tensors[f"{s.name}.router.b"]
         if self.shared is not None:
             self.shared.bind(tensors, rt)
@@ -140,11 +155,27 @@ class RoutedExperts(FeedForward):
         with rt.phase("moe_route", self.w_router, n):
             ops.linear_simt(x, self.w_router, self.b_router, logits)
             ops.moe_route(logits, s.top, ids, weights)
-        act = rt.empty(n * s.top, s.intermediate_size)
-        per_expert = 3.0 * s.intermediate_size * s.hidden_size
-        with rt.phase("moe_experts", nbytes=min(n * s.top, s.n_experts) * per_expert * self.w_gate.element_size(),
-                      flops=2.0 * n * s.top * per_expert):
-            ops.moe_experts(x, self.w_gate, self.w_up, self.w_down, ids, weights, act, residual, s.activation, s.limit)
+        S, f, h = n * s.top, s.intermediate_size, s.hidden_size
+        per_expert = 3.0 * f * h
+        with rt.phase("moe_experts", nbytes=min(S, s.n_experts) * per_expert * self.w_gate.element_size(),
+                      flops=2.0 * S * per_expert):
+            if self.grouped and S > GROUPED_FROM_SLOTS_PER_EXPERT * s.n_experts:
+                # many tokens: sorted by expert, one grouped product each for gate/up (activation in its epilogue) and
+                # down on the tensor cores, then the choices of a token added up in their order
+                act = (s.activation, float(s.limit), 0.0) if s.activation != "silu" else None
+                rows, slots = rt.empty(S, dtype=torch.int32), rt.empty(S, dtype=torch.int32)
+                plan = rt.empty(1 + 3 * ops.moe_plan_tiles(S, s.n_experts), dtype=torch.int32)
+                ops.moe_plan(ids, s.n_experts, rows, slots, plan)
+                xs = rt.empty(S, h, dtype=torch.bfloat16)
+                ops.moe_gather(x, slots, s.top, xs)
+                mid = rt.empty(S, f, dtype=torch.bfloat16)
+                ops.linear_tc_grouped(xs, self.w_gate, mid, plan, s.n_experts, rt.workspace, "swiglu", act)
+                y = rt.empty(S, h, dtype=torch.float32)
+                ops.linear_tc_grouped(mid, self.w_down, y, plan, s.n_experts, rt.workspace)
+                ops.moe_combine(y, rows, weights, residual)
+            else:
+                mid = rt.empty(S, f)
+                ops.moe_experts(x, self.w_gate, self.w_up, self.w_down, ids, weights, mid, residual, s.activation, s.limit)
         if self.shared is not None:
             self.shared.forward(ctx, x, residual)
 

@@ -93,13 +93,20 @@ def rotate(u, positions, base, dims):
     return out
 
 
-def block_mask(T, size):
-    """visible[i, j]: j <= i and both in the same block of ``size`` positions (size 0: every j <= i)."""
-    i, j = np.arange(T)[:, None], np.arange(T)[None, :]
+def masked_attention(q, k, v, q_pos, scale, size=0):
+    """q [n, H, d] at positions q_pos; k [L, G, d] and v [L, G, e] hold the keys and values of positions 0 .. L-1.
+    Head a reads key/value head a // (H / G).  Position i sees j <= i of its own block (size 0: every j <= i)."""
+    n, H, _ = q.shape
+    L, G, e = v.shape
+    i, j = np.asarray(list(q_pos))[:, None], np.arange(L)[None, :]
     vis = j <= i
     if size:
         vis &= (i // size) == (j // size)
-    return vis
+    out = np.zeros((n, H, e))
+    for a in range(H):
+        g = a // (H // G)
+        out[:, a] = softmax_rows((q[:, a] @ k[:, g].T) * scale, vis) @ v[:, g]
+    return out
 
 
 # -- mixers ---------------------------------------------------------------------------------
@@ -115,12 +122,7 @@ def attention(h, w, m, name):
     if rot:
         pos = np.arange(T)
         q, k = rotate(q, pos, rot["base"], rot["dims"]), rotate(k, pos, rot["base"], rot["dims"])
-    vis = block_mask(T, (m.get("mask") or {}).get("size", 0))
-    out = np.zeros((T, H, e))
-    for a in range(H):
-        g = a // (H // G)
-        p = softmax_rows((q[:, a] @ k[:, g].T) * m["scale"], vis)
-        out[:, a] = p @ v[:, g]
+    out = masked_attention(q, k, v, range(T), m["scale"], (m.get("mask") or {}).get("size", 0))
     return out.reshape(T, H * e) @ w[f"{name}.o"].T
 
 
@@ -134,11 +136,7 @@ def latent_attention(h, w, m, name, eps):
     k = (c @ w[f"{name}.uk"].T).reshape(T, H, d)
     v = (c @ w[f"{name}.uv"].T).reshape(T, H, e)
     gate = sigmoid(h @ w[f"{name}.g"].T)            # [T, H]
-    vis = block_mask(T, 0)
-    out = np.zeros((T, H, e))
-    for a in range(H):
-        p = softmax_rows((q[:, a] @ k[:, a].T) * m["scale"], vis)
-        out[:, a] = (p @ v[:, a]) * gate[:, a:a + 1]
+    out = masked_attention(q, k, v, range(T), m["scale"]) * gate[:, :, None]
     return out.reshape(T, H * e) @ w[f"{name}.o"].T
 
 
@@ -202,6 +200,15 @@ def layer_runs(cfg):
     for t in range(times):
         runs += [(i, t if i == a else None) for i in range(a, b)]
     return runs + [(i, None) for i in range(b, n)]
+
+
+def greedy(cfg, w, prompt, n):
+    """n tokens chosen greedily (the first largest logit), the whole sequence recomputed for every token."""
+    seq, out = list(prompt), []
+    for _ in range(n):
+        out.append(int(np.argmax(forward(cfg, w, seq)[-1])))
+        seq.append(out[-1])
+    return out
 
 
 def forward(cfg, w, tokens, trace=None):

@@ -680,7 +680,8 @@ def test_attention_over_pages(ops, nh, nkv, hd, window, dt):
 def test_attention_finds_one_far_key_and_respects_the_window_edge(ops, dt):
     nh, nkv, hd, n = 2, 1, 32, 700
     kp, vp, table, ks, vs = scatter_pages(12, nkv, hd, [n], dt, seed=3)
-    q = torch.randn(1, nh, hd).to(dt)
+    q = torch.randn(1, nh, hd, generator=torch.Generator().manual_seed(11))
+    q = (q / q.norm(dim=-1, keepdim=True) * math.sqrt(hd)).to(dt)      # a query of the usual length, whatever was drawn
     # make key 3 (far back, first page) the one that matters: aligned with q and large
     far = 3
     page, row = int(table[0, far // PAGE]), far % PAGE
