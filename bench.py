@@ -14,8 +14,8 @@ with host token ids in and out.  The line also carries a prefill measurement (on
 64, and the SM clocks sampled during the timed region.
 
 ``--workload NAME`` runs another measurement instead and prints its own JSON: ``14b-unequal``, ``32b`` and
-``long-context`` (larger Qwen3 sizes end to end), and ``romepel`` (the Romepel design at two widths beside Qwen3 layers
-of equal size: a 2 048-token prompt, decode at batch 8, and every phase's time and roofline fraction).
+``long-context`` (larger Qwen3 sizes end to end), and ``romepel`` / ``zevivik`` (those designs at two widths beside Qwen3
+layers of equal size: a 2 048-token prompt, decode at batch 8, and every phase's time and roofline fraction).
 """
 from __future__ import annotations
 
@@ -233,6 +233,7 @@ WORKLOADS = {
     "32b": dict(model="32b", batch=8, prompt=(2048, 2048), decode=512),
     "long-context": dict(model="8b"),
     "romepel": dict(model="8b"),
+    "zevivik": dict(model="8b"),
 }
 
 # `--workload romepel`: the Romepel design (recurrent gla layers, windowed attention with a distance bias, sandwich
@@ -262,6 +263,42 @@ def romepel_configs(z: dict):
                                  intermediate_size=z["inter"], vocab_size=z["vocab"], use_sliding_window=True,
                                  sliding_window=z["window"], max_window_layers=0))
     return rom, qwen
+
+
+# `--workload zevivik`: the Zevivik design (attention inside blocks of positions, latent attention, parallel blocks,
+# routed experts with a shared one, a looped range of layers) at sizes that resemble a real model's layers, beside Qwen3
+# layers of equal width, layer runs, head counts, span and active feed-forward width (top x expert + shared = gated).
+ZEVIVIK_SIZES = {
+    "2048": dict(width=2048, layers=8, heads=16, kv_heads=4, dim=128, inter=6144, window=1024, lat_heads=16, lat_dim=128,
+                 lat_vdim=128, rank=128, experts=16, top=2, vocab=32768),
+    "4096": dict(width=4096, layers=8, heads=32, kv_heads=8, dim=128, inter=12288, window=1024, lat_heads=16, lat_dim=128,
+                 lat_vdim=256, rank=128, experts=16, top=2, vocab=65536),
+}
+
+
+def zevivik_configs(z: dict):
+    """(Zevivik configuration, the closest existing model's: Qwen3 with every layer on a sliding window of the block's
+    size).  Six layers of which the second and third run twice: eight layer runs, five of them with routed experts."""
+    from nncpu_b200.config import config_from_dict
+    dense = {"kind": "dense", "ff": z["inter"]}
+    moe = {"kind": "moe", "expert": {"ff": z["inter"] // 4, "limit": 7.0}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["inter"] // 2, "limit": 7.0}}
+    def att(mlp):
+        return {"type": "attention", "mlp": mlp,
+                "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                          "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}, "rot": {"base": 1000000.0, "dims": z["dim"]}}}
+    def lat(mlp):
+        return {"type": "latent_attention", "mlp": mlp,
+                "mixer": {"heads": z["lat_heads"], "dim": z["lat_dim"], "vdim": z["lat_vdim"], "kv_rank": z["rank"],
+                          "scale": z["lat_dim"] ** -0.5}}
+    layers = [att(dense), att(moe), lat(moe), att(moe), lat(dense), att(dense)]
+    zev = config_from_dict({"architecture": "Zevivik", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+                            "embedding": {"scale": 1.0}, "loop": {"start": 1, "stop": 3, "times": 2}, "layers": layers})
+    qwen = config_from_dict(dict(QWEN3_8B, num_hidden_layers=z["layers"], hidden_size=z["width"],
+                                 num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
+                                 intermediate_size=z["inter"], vocab_size=z["vocab"], use_sliding_window=True,
+                                 sliding_window=z["window"], max_window_layers=0))
+    return zev, qwen
 
 
 def phase_table(totals: dict, calls: int, pk: dict) -> dict:
@@ -342,6 +379,17 @@ def run_romepel() -> dict:
     for name, z in ROMEPEL_SIZES.items():
         rom, qwen = romepel_configs(z)
         out["sizes"][name] = {"config": z, "romepel": run_design_point(rom, z["vocab"], pk),
+                              "qwen3_same_size": run_design_point(qwen, z["vocab"], pk)}
+    return out
+
+
+def run_zevivik() -> dict:
+    pk = peaks()
+    out = {"workload": "zevivik", "dtype": "bf16", "peaks": pk["source"], "prompt": PROMPT,
+           "data": "synthetic: random weights, uniform random token ids", "sizes": {}}
+    for name, z in ZEVIVIK_SIZES.items():
+        zev, qwen = zevivik_configs(z)
+        out["sizes"][name] = {"config": z, "zevivik": run_design_point(zev, z["vocab"], pk),
                               "qwen3_same_size": run_design_point(qwen, z["vocab"], pk)}
     return out
 
@@ -510,7 +558,7 @@ def main() -> int:
         print(json.dumps(fp32_check(cfg, args.model)))
         return 0
     if args.workload:
-        special = {"long-context": run_long_context, "romepel": run_romepel}
+        special = {"long-context": run_long_context, "romepel": run_romepel, "zevivik": run_zevivik}
         print(json.dumps(special[args.workload]() if args.workload in special else run_workload(args.workload)))
         return 0
     model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")

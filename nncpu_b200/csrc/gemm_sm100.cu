@@ -1806,10 +1806,10 @@ extern "C" int nncpu_linear_tc_wait_probe(const void* X, const void* W, float* o
 // k-blocks dealt out evenly over the SMs; 17 to 64 tokens a cluster per output tile); kPlanEvenFrom17: dealt out
 // evenly from 17 tokens on; kPlanNeverEven: never dealt out evenly; kPlanNoPairs: one SM per 128 x 256 tile;
 // kPlanNarrowUnits: units of 128 weight rows where 256 would be taken.
-template <int kEpi>
+template <int BN, int kStages, int kEpi>
 int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, const GroupPlan& g, cudaStream_t stream) {
-    constexpr int BN = 128, kStages = 6;
     constexpr size_t smem = smem_bytes<BN, kStages>();
+    static_assert(smem <= 227 * 1024, "the stages fit shared memory");
     static bool configured[64] = {};
     if (first_use_on_this_device(configured)) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_grouped_kernel<BN, kStages, kEpi>,
@@ -1849,14 +1849,18 @@ extern "C" int nncpu_linear_tc_grouped(const void* X, const void* W, void* C, in
     p.vec = ((uintptr_t)C % 16 == 0) && ((size_t)ldc * esize % 16 == 0);
     p.swap = 0;
     p.rows_a = S; p.rows_b = N;
-    p.tiles_b = (N + 127) / 128;
+    const int bn = N >= 256 ? 256 : 128;       // 128 x 256 tiles where a group's matrix has the rows for them
+    p.tiles_b = (N + bn - 1) / bn;
     p.nf.act = act; p.nf.act_a = act_a;
     CUtensorMap ma, mb;
     if (int e = g_maps.get(&ma, X, S, K, lda, kBlockM)) return e;
-    if (int e = g_maps.get(&mb, W, n_groups * N, K, K, 128)) return e;
+    if (int e = g_maps.get(&mb, W, n_groups * N, K, K, bn)) return e;
     GroupPlan g{n_tiles, tile_group, tile_row0, tile_row_end, max_tiles};
-    return epilogue == kSwiglu ? launch_grouped<kSwiglu>(ma, mb, p, g, (cudaStream_t)stream)
-                               : launch_grouped<kPlain>(ma, mb, p, g, (cudaStream_t)stream);
+    if (bn == 256)
+        return epilogue == kSwiglu ? launch_grouped<256, 4, kSwiglu>(ma, mb, p, g, (cudaStream_t)stream)
+                                   : launch_grouped<256, 4, kPlain>(ma, mb, p, g, (cudaStream_t)stream);
+    return epilogue == kSwiglu ? launch_grouped<128, 6, kSwiglu>(ma, mb, p, g, (cudaStream_t)stream)
+                               : launch_grouped<128, 6, kPlain>(ma, mb, p, g, (cudaStream_t)stream);
 }
 
 enum Plan : int { kPlanEvenFrom17 = 1, kPlanNeverEven = 2, kPlanNoPairs = 4, kPlanNarrowUnits = 8 };

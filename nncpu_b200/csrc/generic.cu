@@ -1581,10 +1581,63 @@ rmsnorm_dual_kernel(const float* __restrict__ x, const void* __restrict__ g1, co
     }
 }
 
+// The common case: a width that is a multiple of 4 and at most 256 * 4 * kVec; every thread keeps its part of the row
+// in registers between the sum of squares and the two scalings, so the row is read once, 16 bytes at a time.
+template <int kVec>
+__global__ void __launch_bounds__(256)
+rmsnorm_dual_f32_kernel(const float* __restrict__ x, const void* __restrict__ g1, const void* __restrict__ g2, int g_dt,
+                        float eps1, float eps2, void* __restrict__ y1, void* __restrict__ y2, int y_dt, int dim) {
+    __shared__ float scratch[33];
+    const int n4 = dim >> 2;
+    const float4* src = reinterpret_cast<const float4*>(x + (size_t)blockIdx.x * dim);
+    float4 v[kVec];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+        const int i = threadIdx.x + j * 256;
+        v[j] = i < n4 ? src[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+        ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float mean = ss * (1.0f / (float)dim);
+    const float s1 = 1.0f / sqrtf(mean + eps1), s2 = 1.0f / sqrtf(mean + eps2);
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i >= n4) continue;
+        const float in[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+        const size_t at = (size_t)blockIdx.x * dim + 4 * i;
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+            const void* g = which ? g2 : g1;
+            void* y = which ? y2 : y1;
+            const float sc = which ? s2 : s1;
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = (in[e] * sc) * ld_f(g, 4 * i + e, g_dt);
+            if (y_dt == DT_BF16) {
+                __nv_bfloat162 h[2] = {__floats2bfloat162_rn(o[0], o[1]), __floats2bfloat162_rn(o[2], o[3])};
+                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(y) + at) = *reinterpret_cast<uint2*>(h);
+            } else {
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(y) + at) = make_float4(o[0], o[1], o[2], o[3]);
+            }
+        }
+    }
+}
+
 extern "C" int nncpu_rmsnorm_dual(const float* x, const void* g1, const void* g2, int g_dt, float eps1, float eps2,
                                   void* y1, void* y2, int y_dt, int n_rows, int dim, void* stream) {
     NN_CHECK(n_rows >= 0 && dim > 0, "rmsnorm (two outputs): %d rows of %d", n_rows, dim);
     if (n_rows == 0) return 0;
+    if (dim % 4 == 0 && dim >= 512 && dim <= 256 * 4 * 8 && (uintptr_t)x % 16 == 0 && (uintptr_t)y1 % 16 == 0 &&
+        (uintptr_t)y2 % 16 == 0) {
+        const auto kernel = dim <= 256 * 4 * 2 ? rmsnorm_dual_f32_kernel<2> : dim <= 256 * 4 * 4 ? rmsnorm_dual_f32_kernel<4>
+                                                                                                    : rmsnorm_dual_f32_kernel<8>;
+        kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>(x, g1, g2, g_dt, eps1, eps2, y1, y2, y_dt, dim);
+        NN_LAUNCH_OK("rmsnorm (two outputs)");
+        return 0;
+    }
     rmsnorm_dual_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>(x, g1, g2, g_dt, eps1, eps2, y1, y2, y_dt, dim);
     NN_LAUNCH_OK("rmsnorm (two outputs)");
     return 0;
@@ -1724,16 +1777,9 @@ extern "C" int nncpu_latent_append(const float* proj, int ld, int col, const voi
 // ---------------------------------------------------------------------------
 constexpr int kRouteMaxExperts = 1024;
 
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, int n_tok, int n_experts, int top, int* __restrict__ ids,
-                 float* __restrict__ weights) {
-    extern __shared__ float smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (t >= n_tok) return;
-    float* z = smem + (size_t)warp * n_experts;
-    for (int e = lane; e < n_experts; e += 32) z[e] = logits[(size_t)t * n_experts + e];
-    __syncwarp();
+// One warp picks the top of z[0 .. n_experts) (shared memory; taken entries are overwritten).
+__device__ __forceinline__ void route_top(float* z, int n_experts, int top, int* __restrict__ ids,
+                                          float* __restrict__ weights, int lane) {
     float z_first = 0.0f, sum = 0.0f;
     for (int c = 0; c < top; ++c) {
         float best = -INFINITY;
@@ -1753,14 +1799,27 @@ moe_route_kernel(const float* __restrict__ logits, int n_tok, int n_experts, int
         const float w = expf(best - z_first);
         sum += w;
         if (lane == 0) {
-            ids[(size_t)t * top + c] = at;
-            weights[(size_t)t * top + c] = w;
+            ids[c] = at;
+            weights[c] = w;
             z[at] = __int_as_float(0x7FC00000);   // taken: NaN loses every comparison above
         }
         __syncwarp();
     }
     const float inv = 1.0f / sum;
-    for (int c = lane; c < top; c += 32) weights[(size_t)t * top + c] *= inv;
+    for (int c = lane; c < top; c += 32) weights[c] *= inv;
+}
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int n_tok, int n_experts, int top, int* __restrict__ ids,
+                 float* __restrict__ weights) {
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= n_tok) return;
+    float* z = smem + (size_t)warp * n_experts;
+    for (int e = lane; e < n_experts; e += 32) z[e] = logits[(size_t)t * n_experts + e];
+    __syncwarp();
+    route_top(z, n_experts, top, ids + (size_t)t * top, weights + (size_t)t * top, lane);
 }
 
 extern "C" int nncpu_moe_route(const float* logits, int n_tok, int n_experts, int top, int* ids, float* weights,
@@ -1778,23 +1837,64 @@ extern "C" int nncpu_moe_route(const float* logits, int n_tok, int n_experts, in
 __device__ __forceinline__ float warp_dot(const void* __restrict__ w, size_t row_at, int w_dt, const float* __restrict__ x,
                                           int k, int lane) {
     float acc = 0.0f;
-    if (w_dt == DT_BF16 && (k & 7) == 0) {
+    if (w_dt == DT_BF16 && (k & 7) == 0 && (row_at & 7) == 0) {
         const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(w) + row_at);
-        for (int i = lane; i < (k >> 3); i += 32) {
-            const uint4 v = src[i];
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-            const float* xs = x + 8 * i;
+        const int n8 = k >> 3;
+        // four 16-byte loads of a lane are asked for before the first is used
+        for (int i0 = lane; i0 < n8; i0 += 128) {
+            uint4 v[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 f = __bfloat1622float2(h[j]);
-                acc = fmaf(f.x, xs[2 * j], acc);
-                acc = fmaf(f.y, xs[2 * j + 1], acc);
+            for (int u = 0; u < 4; ++u) v[u] = i0 + 32 * u < n8 ? src[i0 + 32 * u] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (i0 + 32 * u >= n8) break;
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+                const float* xs = x + 8 * (i0 + 32 * u);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(h[j]);
+                    acc = fmaf(f.x, xs[2 * j], acc);
+                    acc = fmaf(f.y, xs[2 * j + 1], acc);
+                }
             }
         }
     } else {
         for (int i = lane; i < k; i += 32) acc = fmaf(ld_f(w, row_at + i, w_dt), x[i], acc);
     }
     return warp_sum(acc);
+}
+
+// The router in one launch: z = W_r x + b in 32-bit (a warp per expert's row, lanes across k), then the choice.
+// One block per token; x [n_tok, width] of either type, W_r [n_experts, width], b [n_experts].
+__global__ void __launch_bounds__(128)
+moe_router_kernel(const void* __restrict__ x, int x_dt, const void* __restrict__ w, int w_dt, const void* __restrict__ bias,
+                  int b_dt, int n_experts, int top, int width, int* __restrict__ ids, float* __restrict__ weights) {
+    extern __shared__ float smem[];          // the token's input, then its logits
+    float* z = smem + width;
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) smem[i] = ld_f(x, (size_t)t * width + i, x_dt);
+    __syncthreads();
+    for (int e = warp; e < n_experts; e += 4) {
+        const float d = warp_dot(w, (size_t)e * width, w_dt, smem, width, lane);
+        if (lane == 0) z[e] = d + (bias ? ld_f(bias, e, b_dt) : 0.0f);
+    }
+    __syncthreads();
+    if (warp == 0) route_top(z, n_experts, top, ids + (size_t)t * top, weights + (size_t)t * top, lane);
+}
+
+extern "C" int nncpu_moe_router_fits(int n_experts, int width) {
+    return n_experts > 0 && n_experts <= kRouteMaxExperts && (size_t)(width + n_experts) * 4 <= 48 * 1024;
+}
+
+extern "C" int nncpu_moe_router(const void* x, int x_dt, const void* w, int w_dt, const void* bias, int b_dt, int n_tok,
+                                int n_experts, int top, int width, int* ids, float* weights, void* stream) {
+    NN_CHECK(n_tok >= 0 && width > 0 && top > 0 && top <= n_experts && nncpu_moe_router_fits(n_experts, width),
+             "router: %d tokens of %d, the top %d of %d experts", n_tok, width, top, n_experts);
+    if (n_tok == 0) return 0;
+    moe_router_kernel<<<n_tok, 128, (size_t)(width + n_experts) * 4, (cudaStream_t)stream>>>(
+        x, x_dt, w, w_dt, bias, b_dt, n_experts, top, width, ids, weights);
+    NN_LAUNCH_OK("router");
+    return 0;
 }
 
 constexpr int kMoeWarps = 8;

@@ -572,6 +572,21 @@ def moe_route(logits, top: int, ids, weights) -> None:
     _call("generic", "nncpu_moe_route", _ptr(logits), _i(n), _i(E), _i(top), _ptr(ids), _ptr(weights), _stream())
 
 
+def moe_router_fits(n_experts: int, width: int) -> bool:
+    """Whether ``moe_router`` takes these sizes (a token's input and logits in one block's shared memory)."""
+    return 0 < n_experts <= 1024 and (width + n_experts) * 4 <= 48 * 1024
+
+
+def moe_router(x, w, bias, top: int, ids, weights) -> None:
+    """The router in one launch: logits = x . w^T + bias in 32-bit, then ``moe_route``'s choice and weights."""
+    n, width = x.shape
+    E = w.shape[0]
+    assert w.shape == (E, width) and (bias is None or bias.numel() == E) and ids.shape == weights.shape == (n, top)
+    assert ids.dtype == torch.int32 and weights.dtype == torch.float32
+    _call("generic", "nncpu_moe_router", _ptr(x), _i(_code(x)), _ptr(w), _i(_code(w)), _ptr(bias), _i(_code(bias)), _i(n),
+          _i(E), _i(top), _i(width), _ptr(ids), _ptr(weights), _stream())
+
+
 def moe_experts(x, w_gate, w_up, w_down, ids, weights, act, out, kind: str, limit: float = 0.0) -> None:
     """out[t] += sum_c weights[t, c] * W_down[e] act(W_gate[e] x_t, W_up[e] x_t) with e = ids[t, c].  Weights are
     [E, ff, width] (gate, up) and [E, width, ff] (down); with ``w_up`` None, ``w_gate`` is [E, 2 ff, width] with an

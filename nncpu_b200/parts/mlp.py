@@ -149,32 +149,39 @@ class RoutedExperts(FeedForward):
         n = x.shape[0]
         if getattr(ctx, "branch_is_fresh", False):
             raise UnsupportedModel(f"{s.name}: routed experts add into the stream they are given")
-        logits = rt.empty(n, s.n_experts, dtype=torch.float32)
         ids = rt.empty(n, s.top, dtype=torch.int32)
         weights = rt.empty(n, s.top, dtype=torch.float32)
         with rt.phase("moe_route", self.w_router, n):
-            ops.linear_simt(x, self.w_router, self.b_router, logits)
-            ops.moe_route(logits, s.top, ids, weights)
+            if ops.moe_router_fits(s.n_experts, s.hidden_size):
+                ops.moe_router(x, self.w_router, self.b_router, s.top, ids, weights)
+            else:
+                logits = rt.empty(n, s.n_experts, dtype=torch.float32)
+                ops.linear_simt(x, self.w_router, self.b_router, logits)
+                ops.moe_route(logits, s.top, ids, weights)
         S, f, h = n * s.top, s.intermediate_size, s.hidden_size
-        per_expert = 3.0 * f * h
-        with rt.phase("moe_experts", nbytes=min(S, s.n_experts) * per_expert * self.w_gate.element_size(),
-                      flops=2.0 * S * per_expert):
-            if self.grouped and S > GROUPED_FROM_SLOTS_PER_EXPERT * s.n_experts:
-                # many tokens: sorted by expert, one grouped product each for gate/up (activation in its epilogue) and
-                # down on the tensor cores, then the choices of a token added up in their order
-                act = (s.activation, float(s.limit), 0.0) if s.activation != "silu" else None
+        esize = self.w_gate.element_size()
+        experts_read = min(S, s.n_experts)
+        if self.grouped and S > GROUPED_FROM_SLOTS_PER_EXPERT * s.n_experts:
+            # many tokens: sorted by expert, one grouped product each for gate/up (activation in its epilogue) and
+            # down on the tensor cores, then the choices of a token added up in their order
+            act = (s.activation, float(s.limit), 0.0) if s.activation != "silu" else None
+            with rt.phase("moe_sort", nbytes=4.0 * S * h):
                 rows, slots = rt.empty(S, dtype=torch.int32), rt.empty(S, dtype=torch.int32)
                 plan = rt.empty(1 + 3 * ops.moe_plan_tiles(S, s.n_experts), dtype=torch.int32)
                 ops.moe_plan(ids, s.n_experts, rows, slots, plan)
                 xs = rt.empty(S, h, dtype=torch.bfloat16)
                 ops.moe_gather(x, slots, s.top, xs)
-                mid = rt.empty(S, f, dtype=torch.bfloat16)
+            mid = rt.empty(S, f, dtype=torch.bfloat16)
+            with rt.phase("moe_gate_up", nbytes=experts_read * 2.0 * f * h * esize, flops=4.0 * S * f * h):
                 ops.linear_tc_grouped(xs, self.w_gate, mid, plan, s.n_experts, rt.workspace, "swiglu", act)
-                y = rt.empty(S, h, dtype=torch.float32)
+            y = rt.empty(S, h, dtype=torch.float32)
+            with rt.phase("moe_down", nbytes=experts_read * 1.0 * f * h * esize + 4.0 * S * h, flops=2.0 * S * f * h):
                 ops.linear_tc_grouped(mid, self.w_down, y, plan, s.n_experts, rt.workspace)
+            with rt.phase("moe_combine", nbytes=4.0 * S * h + 8.0 * n * h):
                 ops.moe_combine(y, rows, weights, residual)
-            else:
-                mid = rt.empty(S, f)
+        else:
+            mid = rt.empty(S, f)
+            with rt.phase("moe_experts", nbytes=experts_read * 3.0 * f * h * esize, flops=6.0 * S * f * h):
                 ops.moe_experts(x, self.w_gate, self.w_up, self.w_down, ids, weights, mid, residual, s.activation, s.limit)
         if self.shared is not None:
             self.shared.forward(ctx, x, residual)
