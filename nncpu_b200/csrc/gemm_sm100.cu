@@ -407,7 +407,28 @@ struct GroupPlan {
     const int* tile_row0;     // [max tiles] its first row of A (and of C)
     const int* tile_row_end;  // [max tiles] the end of its group's rows
     int max_tiles;
+    // The other kind of groups (no plan on the device, uniform_rows > 0): every group has all uniform_rows rows of A,
+    // but its own columns: group e reads the K columns of A from column e * a_col_step and writes its N columns of C
+    // from column e * c_col_step (one small product per head of a mixer).  max_tiles is then groups x tiles of rows.
+    int uniform_rows;
+    int a_col_step, c_col_step;
+    const float* gate;        // or null: row r of group e is multiplied by sigmoid(gate[r * gate_ld + gate_col + e])
+    int gate_ld, gate_col;
 };
+
+// Tile `ta` of a grouped product: its group, first row and the end of the rows that count.
+__device__ __forceinline__ void group_tile(const GroupPlan& g, int ta, int& group, int& row0, int& row_end) {
+    if (g.uniform_rows > 0) {
+        const int per = (g.uniform_rows + kBlockM - 1) / kBlockM;
+        group = ta / per;
+        row0 = (ta % per) * kBlockM;
+        row_end = g.uniform_rows;
+    } else {
+        group = g.tile_group[ta];
+        row0 = g.tile_row0[ta];
+        row_end = g.tile_row_end[ta];
+    }
+}
 
 template <int BN, int kStages, int kEpi>
 __global__ void __launch_bounds__(kThreads)
@@ -428,7 +449,7 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_a = min(*g.n_tiles, g.max_tiles);
+    const int tiles_a = g.uniform_rows > 0 ? g.max_tiles : min(*g.n_tiles, g.max_tiles);
     const int n_tiles = tiles_a * p.tiles_b;
     const unsigned long long limit = p.wait_ns ? p.wait_ns : kWaitLimitNs;
     const int my_tiles = (int)blockIdx.x < n_tiles ? (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -465,8 +486,9 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             for (int r = 0; r < my_runs; ++r) {
                 const int w = blockIdx.x + (r / p.kb_total) * gridDim.x, kb = r % p.kb_total;
-                const int ta = w % tiles_a;
-                const int m0 = g.tile_row0[ta], n0 = g.tile_group[ta] * p.rows_b + (w / tiles_a) * BN;
+                int group, m0, row_end;
+                group_tile(g, w % tiles_a, group, m0, row_end);
+                const int n0 = group * p.rows_b + (w / tiles_a) * BN;
                 const int s = r % kStages;
                 if (r >= kStages && !mbar_wait(&empty[s], ((r / kStages) & 1) ^ 1, limit)) {
                     atomicExch(p.status, kTimeoutEmpty);
@@ -474,7 +496,7 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     break;
                 }
                 mbar_expect_tx(&full[s], kBytesA + kBytesB);
-                tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], kb * kBlockK, m0);
+                tma_load_2d(smem_a + s * kBytesA, &map_a, &full[s], group * g.a_col_step + kb * kBlockK, m0);
                 tma_load_2d(smem_b + s * kBytesB, &map_b, &full[s], kb * kBlockK, n0);
                 issued = r + 1;
             }
@@ -524,9 +546,14 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         GemmParams q = p;                 // rows_a becomes the end of the tile's group: rows beyond it are not stored
         int it = 0;
         for (int w = blockIdx.x; w < n_tiles; w += gridDim.x, ++it) {
-            const int ta = w % tiles_a;
-            const int a_row = g.tile_row0[ta] + row_in_tile, n0 = (w / tiles_a) * BN;
-            q.rows_a = g.tile_row_end[ta];
+            int group, row0, row_end;
+            group_tile(g, w % tiles_a, group, row0, row_end);
+            const int col_off = group * g.c_col_step;
+            const int a_row = row0 + row_in_tile, n0 = col_off + (w / tiles_a) * BN;
+            q.rows_a = row_end;
+            q.rows_b = col_off + p.rows_b;
+            const float scale = (g.gate != nullptr && a_row < row_end)
+                ? 1.0f / (1.0f + expf(0.0f - g.gate[(size_t)a_row * g.gate_ld + g.gate_col + group])) : 1.0f;
             const int buf = it & 1;
             if (!mbar_wait(&acc_full[buf], (it >> 1) & 1, limit)) {
                 if (lane == 0) atomicExch(p.status, kTimeoutAccumFull);
@@ -539,6 +566,10 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 float v[16];
                 tmem_ld16(taddr + (uint32_t)c0, v);
+                if (g.gate != nullptr) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] *= scale;
+                }
                 store16<kEpi>(q, a_row, n0 + c0, v);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -1855,12 +1886,53 @@ extern "C" int nncpu_linear_tc_grouped(const void* X, const void* W, void* C, in
     CUtensorMap ma, mb;
     if (int e = g_maps.get(&ma, X, S, K, lda, kBlockM)) return e;
     if (int e = g_maps.get(&mb, W, n_groups * N, K, K, bn)) return e;
-    GroupPlan g{n_tiles, tile_group, tile_row0, tile_row_end, max_tiles};
+    GroupPlan g{};
+    g.n_tiles = n_tiles; g.tile_group = tile_group; g.tile_row0 = tile_row0; g.tile_row_end = tile_row_end;
+    g.max_tiles = max_tiles;
     if (bn == 256)
         return epilogue == kSwiglu ? launch_grouped<256, 4, kSwiglu>(ma, mb, p, g, (cudaStream_t)stream)
                                    : launch_grouped<256, 4, kPlain>(ma, mb, p, g, (cudaStream_t)stream);
     return epilogue == kSwiglu ? launch_grouped<128, 6, kSwiglu>(ma, mb, p, g, (cudaStream_t)stream)
                                : launch_grouped<128, 6, kPlain>(ma, mb, p, g, (cudaStream_t)stream);
+}
+
+// One small product per head on the tensor cores: C[m, e * c_step + j] = sum_k X[m, e * a_step + k] W[e, j, k] for the
+// heads e < n_heads, j < N, k < K, every row m < M; with `gate` (32-bit logits [M, gate_ld]) row m of head e is
+// multiplied by sigmoid(gate[m, gate_col + e]).  X [M, lda] and W [n_heads, N, K] bfloat16.  K must be a multiple of 64
+// (a k-block of a head must not reach into the next head's columns) and a_step of 8.
+extern "C" int nncpu_linear_tc_heads_supported(int N, int K, int a_step, int lda) {
+    return N > 0 && K > 0 && K % 64 == 0 && a_step % 8 == 0 && lda % 8 == 0;
+}
+
+extern "C" int nncpu_linear_tc_heads(const void* X, const void* W, void* C, int c_dt, int M, int N, int K, int n_heads,
+                                     int lda, int ldc, int a_step, int c_step, const float* gate, int gate_ld,
+                                     int gate_col, int* status, void* stream) {
+    NN_CHECK(M > 0 && n_heads > 0 && nncpu_linear_tc_heads_supported(N, K, a_step, lda) && (long)n_heads * N < (1l << 31),
+             "gemm (per head): M %d, %d heads of %d x %d, a_step %d, lda %d", M, n_heads, N, K, a_step, lda);
+    NN_CHECK(lda >= (n_heads - 1) * a_step + K && ldc >= (n_heads - 1) * c_step + N && c_step >= N,
+             "gemm (per head): row strides %d / %d for %d heads", lda, ldc, n_heads);
+    NN_CHECK(((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0, "gemm (per head): operands must be 16-byte aligned");
+    NN_CHECK(gate == nullptr || gate_ld >= gate_col + n_heads, "gemm (per head): gate stride %d", gate_ld);
+    GemmParams p{};
+    p.K = K;
+    p.kb_total = K / kBlockK;
+    p.out = C; p.out_dt = c_dt; p.ldc = ldc; p.status = status;
+    const int esize = c_dt == DT_F32 ? 4 : 2;
+    p.vec = ((uintptr_t)C % 16 == 0) && ((size_t)ldc * esize % 16 == 0) && ((size_t)c_step * esize % 16 == 0);
+    p.swap = 0;
+    p.rows_a = M; p.rows_b = N;
+    const int bn = N >= 256 ? 256 : 128;
+    p.tiles_b = (N + bn - 1) / bn;
+    CUtensorMap ma, mb;
+    if (int e = g_maps.get(&ma, X, M, (n_heads - 1) * a_step + K, lda, kBlockM)) return e;
+    if (int e = g_maps.get(&mb, W, n_heads * N, K, K, bn)) return e;
+    GroupPlan g{};
+    g.uniform_rows = M;
+    g.max_tiles = n_heads * ((M + kBlockM - 1) / kBlockM);
+    g.a_col_step = a_step; g.c_col_step = c_step;
+    g.gate = gate; g.gate_ld = gate_ld; g.gate_col = gate_col;
+    return bn == 256 ? launch_grouped<256, 4, kPlain>(ma, mb, p, g, (cudaStream_t)stream)
+                     : launch_grouped<128, 6, kPlain>(ma, mb, p, g, (cudaStream_t)stream);
 }
 
 enum Plan : int { kPlanEvenFrom17 = 1, kPlanNeverEven = 2, kPlanNoPairs = 4, kPlanNarrowUnits = 8 };

@@ -1731,15 +1731,20 @@ extern "C" int nncpu_linear_heads(const void* A, int a_dt, const void* W, int w_
 // ---------------------------------------------------------------------------
 // Latent attention keeps one vector per position: c = rmsnorm(z) * gamma of `rank` lanes, where z sits at column
 // `col` of the rows of proj [n_tok, ld] (32-bit).  It goes to the token's row of the key pages (one key/value head
-// of `rank` lanes); the same pages serve as values.  One block per token.
+// of `rank` lanes); the same pages serve as values.  One block per token.  With q_out (bfloat16 [n_tok, q_size]) the
+// first q_size columns of the token's row (the queries) are copied there rounded to bfloat16, for the per-head
+// products on the tensor cores.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(128)
 latent_append_kernel(const float* __restrict__ proj, int ld, int col, const void* __restrict__ gamma, int g_dt,
                      float eps, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                      const int* __restrict__ block_table, int bt_stride, void* __restrict__ pages, int kv_dt,
-                     int rank) {
+                     int rank, __nv_bfloat16* __restrict__ q_out, int q_size) {
     __shared__ float scratch[33];
     const int t = blockIdx.x;
+    if (q_out != nullptr)
+        for (int i = threadIdx.x; i < q_size; i += blockDim.x)
+            q_out[(size_t)t * q_size + i] = __float2bfloat16_rn(proj[(size_t)t * ld + i]);
     const int seq = tok_seq[t];
     if (seq < 0) return;                    // a padded row owns no place in the cache
     const float* z = proj + (size_t)t * ld + col;
@@ -1756,12 +1761,14 @@ latent_append_kernel(const float* __restrict__ proj, int ld, int col, const void
 
 extern "C" int nncpu_latent_append(const float* proj, int ld, int col, const void* gamma, int g_dt, float eps,
                                    const int* tok_seq, const int* tok_pos, const int* block_table, int bt_stride,
-                                   void* pages, int kv_dt, int n_tok, int rank, void* stream) {
+                                   void* pages, int kv_dt, int n_tok, int rank, void* q_out, int q_size, void* stream) {
     NN_CHECK(n_tok >= 0 && rank > 0 && col >= 0 && ld >= col + rank, "latent append: %d tokens, rank %d at column %d of %d",
              n_tok, rank, col, ld);
+    NN_CHECK(q_out == nullptr || (q_size > 0 && q_size <= ld), "latent append: %d query lanes of a row of %d", q_size, ld);
     if (n_tok == 0) return 0;
     latent_append_kernel<<<n_tok, 128, 0, (cudaStream_t)stream>>>(proj, ld, col, gamma, g_dt, eps, tok_seq, tok_pos,
-                                                                  block_table, bt_stride, pages, kv_dt, rank);
+                                                                  block_table, bt_stride, pages, kv_dt, rank,
+                                                                  (__nv_bfloat16*)q_out, q_size);
     NN_LAUNCH_OK("latent append");
     return 0;
 }

@@ -552,15 +552,36 @@ def linear_heads(x, x_col: int, w, out, out_col: int = 0, gate=None, gate_col: i
           _i(0 if gate is None else gate.shape[1]), _i(gate_col), _stream())
 
 
-def latent_append(proj, col: int, gamma, eps: float, tok_seq, tok_pos, block_table, pages) -> None:
+def linear_heads_tc_supported(x, x_col: int, w, out) -> bool:
+    """Whether ``linear_heads_tc`` takes these operands: bfloat16 x and w, a head's K a multiple of 64, 16-byte steps."""
+    B, N, K = w.shape
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+            and x_col == 0 and K % 64 == 0 and x.shape[1] % 8 == 0)
+
+
+def linear_heads_tc(x, w, out, workspace: GemmWorkspace, gate=None, gate_col: int = 0) -> None:
+    """``linear_heads`` on the tcgen05 tensor cores (the grouped product with the heads as groups): x [n, >= B K]
+    bfloat16 with the heads side by side from column 0, w [B, N, K] bfloat16, out [n, >= B N] from column 0."""
+    B, N, K = w.shape
+    m = x.shape[0]
+    assert linear_heads_tc_supported(x, 0, w, out) and out.shape[0] == m and x.shape[1] >= B * K and out.shape[1] >= B * N
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape[0] == m and gate.is_contiguous())
+    _call("gemm_sm100", "nncpu_linear_tc_heads", _ptr(x), _ptr(w), _ptr(out), _i(_code(out)), _i(m), _i(N), _i(K), _i(B),
+          _i(x.shape[1]), _i(out.shape[1]), _i(K), _i(N), _ptr(gate), _i(0 if gate is None else gate.shape[1]), _i(gate_col),
+          _ptr(workspace.status), _stream())
+
+
+def latent_append(proj, col: int, gamma, eps: float, tok_seq, tok_pos, block_table, pages, q_out=None) -> None:
     """pages[row of token t] = rmsnorm(proj[t, col : col + rank]) * gamma: the one vector per position that latent
-    attention keeps.  proj float32; pages [n_pages, 1, PAGE, rank]."""
+    attention keeps.  proj float32; pages [n_pages, 1, PAGE, rank].  With ``q_out`` (bfloat16 [n, q_size]) the first
+    q_size columns of proj are left there rounded to bfloat16."""
     n = proj.shape[0]
     rank = pages.shape[-1]
     assert proj.dtype == torch.float32 and pages.shape[1] == 1 and gamma.numel() == rank
+    assert q_out is None or (q_out.dtype == torch.bfloat16 and q_out.shape[0] == n and q_out.shape[1] <= proj.shape[1])
     _call("generic", "nncpu_latent_append", _ptr(proj), _i(proj.shape[1]), _i(col), _ptr(gamma), _i(_code(gamma)), _f(eps),
           _ptr(tok_seq), _ptr(tok_pos), _ptr(block_table), _i(block_table.shape[1]), _ptr(pages), _i(_code(pages)),
-          _i(n), _i(rank), _stream())
+          _i(n), _i(rank), _ptr(q_out), _i(0 if q_out is None else q_out.shape[1]), _stream())
 
 
 def moe_route(logits, top: int, ids, weights) -> None:

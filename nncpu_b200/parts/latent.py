@@ -82,20 +82,30 @@ class LatentAttention(Mixer):
         proj = rt.empty(n, self.proj_size, dtype=torch.float32)
         with rt.phase("attn_qkv", self.w_in, n):
             rt.linear(x, self.w_in, None, proj)
+        fast = self._tensor_core_attention(cache)
+        lat_dt = torch.bfloat16 if fast else torch.float32
+        q_lat, o_lat, heads = rt.empty(n, H * r, dtype=lat_dt), rt.empty(n, H * r, dtype=lat_dt), rt.empty(n, self.out_size)
+        # the two per-head products run on the tensor cores where the sizes allow it (the queries are rounded to
+        # bfloat16 for that, where the norm's kernel passes over the row anyway), else in 32-bit on the CUDA cores
+        q16 = rt.empty(n, self.q_size, dtype=torch.bfloat16)
+        absorb_tc = fast and ops.linear_heads_tc_supported(q16, 0, self.w_uk_t, q_lat)
+        expand_tc = fast and ops.linear_heads_tc_supported(o_lat, 0, self.w_uv, heads)
         with rt.phase("attn_rope"):
             ops.latent_append(proj, self.q_size, self.w_norm, s.eps, ctx.tok_seq, ctx.tok_pos, cache.block_table,
-                              cache.k_pages)
-        fast = self._tensor_core_attention(cache)
-        q_lat = rt.empty(n, H * r, dtype=torch.bfloat16 if fast else torch.float32)
+                              cache.k_pages, q16 if absorb_tc else None)
         with rt.phase("attn_absorb", self.w_uk_t, n):
-            ops.linear_heads(proj, 0, self.w_uk_t, q_lat)
-        o_lat = rt.empty(n, H * r, dtype=torch.bfloat16 if fast else torch.float32)
+            if absorb_tc:
+                ops.linear_heads_tc(q16, self.w_uk_t, q_lat, rt.workspace)
+            else:
+                ops.linear_heads(proj, 0, self.w_uk_t, q_lat)
         with self._core_phase(ctx, cache):
             self._attend(ctx, q_lat, cache, o_lat, fast)
-        heads = rt.empty(n, self.out_size)
+        gate = proj if s.head_gate else None
         with rt.phase("attn_expand", self.w_uv, n):
-            ops.linear_heads(o_lat, 0, self.w_uv, heads, gate=proj if s.head_gate else None,
-                             gate_col=self.q_size + r)
+            if expand_tc:
+                ops.linear_heads_tc(o_lat, self.w_uv, heads, rt.workspace, gate=gate, gate_col=self.q_size + r)
+            else:
+                ops.linear_heads(o_lat, 0, self.w_uv, heads, gate=gate, gate_col=self.q_size + r)
         with rt.phase("attn_out", self.w_o, n):
             rt.linear(heads, self.w_o, None, residual, accumulate=not getattr(ctx, "branch_is_fresh", False),
                       then_norm=getattr(ctx, "next_norm", None))

@@ -282,6 +282,29 @@ def test_one_product_per_head_and_the_sigmoid_gate():
     check(out, want, 2e-6, "per-head product")
 
 
+@pytest.mark.parametrize("n,H,K,N", [(21, 3, 64, 36), (300, 4, 128, 128), (130, 16, 128, 256), (1, 2, 64, 8), (700, 5, 192, 520)])
+def test_one_product_per_head_on_the_tensor_cores(n, H, K, N):
+    """The same as one grouped product with the heads as groups: a head's columns of the input, its own matrix, its
+    columns of the output, the sigmoid gate in the epilogue; bfloat16 and float32 outputs."""
+    from nncpu_b200.parts import Runtime
+    rt = Runtime(DEV, torch.bfloat16)
+    g = torch.Generator().manual_seed(n + N)
+    x = torch.randn(n, H * K, generator=g).bfloat16()
+    w = (torch.randn(H, N, K, generator=g) * 0.1).bfloat16()
+    gate = torch.randn(n, H + 3, generator=g)
+    for out_dt, tol in ((torch.bfloat16, 8e-3), (torch.float32, 1e-5)):
+        for use_gate in (False, True):
+            out = torch.full((n, H * N), float("nan"), dtype=out_dt, device=DEV)
+            assert ops.linear_heads_tc_supported(x, 0, w, out)
+            ops.linear_heads_tc(x.to(DEV), w.to(DEV), out, rt.workspace, gate=gate.to(DEV) if use_gate else None, gate_col=2)
+            rt.check_status()
+            want = np.zeros((n, H * N))
+            for b in range(H):
+                y = x[:, b * K:(b + 1) * K].double().numpy() @ w[b].double().numpy().T
+                want[:, b * N:(b + 1) * N] = y * (P.sigmoid(gate[:, 2 + b].double().numpy())[:, None] if use_gate else 1.0)
+            check(out, want, tol, f"per-head product on the tensor cores, {out_dt}, gate {use_gate}")
+
+
 def test_rotation_of_a_part_of_the_head():
     """The first ``dims`` lanes turn, lane i with lane i + dims/2; the others pass."""
     nh, nkv, hd, dims, base = 3, 1, 24, 10, 777.0
