@@ -22,6 +22,9 @@ GATED_ACTIVATIONS = ("silu", "gelu_tanh", "swish_clamp")
 # below it every slot reads its expert's rows itself.  Measured at 16 experts of 3 x 1536 x 2048 and 3 x 3072 x 4096 with
 # the top 2: one token 56 / 112 us per slot against 103 / 161 us grouped, eight tokens 136 / 419 us against 120 / 265 us.
 GROUPED_FROM_SLOTS = 8
+# From this many tokens the router's logits are a product of their own instead of part of the router's one kernel,
+# in which every token's block reads all of the router's rows.
+ROUTER_PRODUCT_FROM_TOKENS = 256
 
 @register_feed_forward("gated_mlp")
 class GatedMlp(FeedForward):
@@ -152,11 +155,17 @@ class RoutedExperts(FeedForward):
         ids = rt.empty(n, s.top, dtype=torch.int32)
         weights = rt.empty(n, s.top, dtype=torch.float32)
         with rt.phase("moe_route", self.w_router, n):
-            if ops.moe_router_fits(s.n_experts, s.hidden_size):
+            many = n >= ROUTER_PRODUCT_FROM_TOKENS and rt.tensor_cores_take(x.dtype, self.w_router, s.hidden_size)
+            if not many and ops.moe_router_fits(s.n_experts, s.hidden_size):
                 ops.moe_router(x, self.w_router, self.b_router, s.top, ids, weights)
             else:
+                # many tokens: the logits as a product of their own (bfloat16 operands are multiplied exactly and
+                # added in 32-bit on the tensor cores; a float32 run, and sizes those refuse, use the CUDA cores)
                 logits = rt.empty(n, s.n_experts, dtype=torch.float32)
-                ops.linear_simt(x, self.w_router, self.b_router, logits)
+                if many:
+                    rt.linear(x, self.w_router, self.b_router, logits)
+                else:
+                    ops.linear_simt(x, self.w_router, self.b_router, logits)
                 ops.moe_route(logits, s.top, ids, weights)
         S, f, h = n * s.top, s.intermediate_size, s.hidden_size
         esize = self.w_gate.element_size()
