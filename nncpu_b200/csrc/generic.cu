@@ -1966,9 +1966,16 @@ extern "C" int nncpu_moe_experts(const void* x, int x_dt, const void* wg, const 
              n_tok, top, width, ff, n_experts);
     NN_CHECK(kind >= kGateSilu && kind <= kGateSwishClamp, "experts: activation kind %d", kind);
     NN_CHECK(wu != nullptr || ff % 8 == 0, "experts: interleaved gate and up rows need a multiple of 8 of them (%d)", ff);
-    NN_CHECK((size_t)width * 4 <= 48 * 1024 && (size_t)top * ff * 4 <= 48 * 1024,
+    constexpr size_t kMost = 200 * 1024;
+    NN_CHECK((size_t)width * 4 <= kMost && (size_t)top * ff * 4 <= kMost,
              "experts: a token's %d inputs or %d x %d activations do not fit the shared memory of this kernel", width, top, ff);
     if (n_tok == 0) return 0;
+    static bool configured[64] = {};
+    if (first_use_on_this_device(configured)) {
+        cudaError_t e = cudaFuncSetAttribute(moe_gate_up_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMost);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(moe_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMost);
+        NN_CHECK(e == cudaSuccess, "experts: cannot reserve %zu bytes of shared memory: %s", kMost, cudaGetErrorString(e));
+    }
     const long slots = (long)n_tok * top;
     NN_CHECK(slots < (1l << 31), "experts: %ld token slots", slots);
     // few tokens: more blocks per token, so that the weights' stream is spread over the SMs
