@@ -617,6 +617,28 @@ def test_long_decoding_across_blocks_and_pages(folders, dtype):
     engine.cache.check()
 
 
+def test_long_prompt_through_the_fused_projection_epilogue_and_the_grouped_experts(tmp_path):
+    """Head size 128, whole heads rotated, 600 tokens in one step: the q/k/v product's epilogue rotates and appends, the
+    tcgen05 prompt kernel masks by blocks of 200, the experts run as a grouped product; then ten tokens one by one
+    (attention from the projections).  bfloat16 against the plain model, and against the same model run in float32."""
+    cfg = {"architecture": "Zevivik", "vocab": 300, "width": 256, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+           "loop": {"start": 0, "stop": 1, "times": 2},
+           "layers": [att(4, 2, 128, 128, 0.09, size=200, rot=(1000000.0, 128), mlp=moe(4, 2, 64, 2.0, shared=(128, 1.0))),
+                      lat(4, 64, 64, 128, 0.125, mlp=dense(256))]}
+    folder = write_folder(tmp_path / "m", cfg, 5, torch.bfloat16, sharpen=2.0)
+    t = toks(cfg, 610, 3)
+    want = plain_logits(folder, t)
+    rows = list(range(0, 600, 7)) + [198, 199, 200, 201, 399, 400, 599]
+    for dtype in ("bfloat16", "float32"):
+        model = Model.load(folder, dtype=dtype)
+        engine = Engine(model, max_tokens=64 * 11)
+        s = engine.alloc_slot()
+        close(engine.step([s], [t[:600]], [rows]), want[rows], dtype, f"{dtype}: a prompt of 600 tokens")
+        out = torch.cat([engine.step([s], [[t[i]]]).clone() for i in range(600, 610)])
+        close(out, want[600:], dtype, f"{dtype}: ten tokens after it")
+        model.rt.check_status()
+
+
 def test_a_key_far_back_in_a_latent_layer(tmp_path):
     """One latent layer with queries and keys so sharp that single keys take most of a row's weight, most of them far
     back and across pages (560 positions, every key visible): the logits must follow the plain model as a prompt and
