@@ -146,7 +146,7 @@ class BlockSpec:
     x += mixer(norm1(x)); x += feed_forward(norm2(x)).  ``kind`` "sandwich" norms each sublayer's output too:
     x += norm1_post(mixer(norm1(x))); x += norm2_post(feed_forward(norm2(x))), and a layer without a
     feed-forward (``feed_forward`` None) has the first sublayer only.  ``kind`` "parallel": both sublayers read the
-    stream as it enters the layer, x += mixer(norm1(x)) + feed_forward(norm2(x)); without a feed-forward there is no norm2."""
+    stream as it enters the layer, x += mixer(norm1(x)) + feed_forward(norm2(x)); without a feed-forward norm2 is not used (its tensor is optional)."""
     kind: str
     norm1: NormSpec
     mixer: MixerSpec

@@ -261,8 +261,9 @@ class ZevivikConfig:
                 ff = RoutedExpertsSpec(kind="routed_experts", name=f"{p}.mlp", hidden_size=w, intermediate_size=m.ff,
                                        n_experts=m.experts, top=m.top, activation="swish_clamp", limit=m.limit,
                                        shared=shared)
-            blocks.append(BlockSpec(kind="parallel", norm1=norm(f"{p}.norm1"), mixer=mixer,
-                                    norm2=norm(f"{p}.norm2") if ff is not None else None, feed_forward=ff))
+            # a layer without a feed-forward has no use for its second norm; a file that holds one all the same is taken
+            blocks.append(BlockSpec(kind="parallel", norm1=norm(f"{p}.norm1"), mixer=mixer, norm2=norm(f"{p}.norm2"),
+                                    feed_forward=ff))
         return ModelSpec(
             architecture=self.architecture, hidden_size=w, vocab_size=self.vocab, max_positions=self.max_positions,
             embedding=EmbeddingSpec("embed", self.vocab, w, scale=self.embedding_scale, suffix=""),

@@ -190,13 +190,8 @@ class ParallelBlock(Block):
         self.mixer = base.build("mixer", spec.mixer, **kwargs)
         self.feed_forward = None if spec.feed_forward is None else base.build("feed_forward", spec.feed_forward)
         self.norm2 = None if self.feed_forward is None else base.build("norm", spec.norm2)
-        self._spare = None
-        if self.feed_forward is None:
-            n1 = spec.norm1
-            name = spec.norm2.name + spec.norm2.suffix if spec.norm2 is not None else None
-            if name is None and n1.name.endswith("norm1"):
-                name = n1.name[:-1] + "2" + n1.suffix
-            self._spare = name
+        # a layer without a feed-forward may still name its second norm: the tensor is then optional
+        self._spare = spec.norm2.name + spec.norm2.suffix if (self.feed_forward is None and spec.norm2 is not None) else None
         self._parts = tuple(p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None)
 
     def params(self):

@@ -33,7 +33,7 @@ def test_keys_round_trip_and_specs():
     assert config_from_dict(cfg.to_dict()) == cfg and cfg.to_dict() == CFG
     spec = cfg.model_spec()
     a, l, b, z = spec.layers
-    assert {x.kind for x in spec.layers} == {"parallel"} and z.feed_forward is None and z.norm2 is None
+    assert {x.kind for x in spec.layers} == {"parallel"} and z.feed_forward is None
     assert (a.mixer.n_heads, a.mixer.n_kv_heads, a.mixer.head_dim, a.mixer.v_head_dim) == (6, 3, 8, 12)
     assert (a.mixer.chunk, a.mixer.window, a.mixer.scale) == (33, 0, 0.25)
     assert (a.mixer.position.theta, a.mixer.position.rotary_dim) == (1234.0, 6)
